@@ -25,13 +25,13 @@ from transformers import GenerationMixin, PreTrainedConfig, PreTrainedModel
 from transformers.modeling_outputs import CausalLMOutputWithPast
 
 from ipex_llm_b200.transformers.kv import DynamicStateCache
-from ipex_llm_b200.transformers.models import mixer_ops as ops
+from ipex_llm_b200.transformers.models import experts, mixer_ops as ops
 from ipex_llm_b200.transformers.models.common import merge_linear
 from ipex_llm_b200.transformers.models.utils import read_safetensors
 from ipex_llm_b200.utils.common import invalidInputError
 
 ABSORB_MAX_TOKENS = 16        # up to this many new tokens per row attend to the latent cache itself (no key / value expansion)
-MOE_SMALL_TOKENS = 32         # up to this many tokens take the experts' host-free path
+MOE_SMALL_TOKENS = experts.MOE_SMALL_TOKENS
 
 
 class SerotarConfig(PreTrainedConfig):
@@ -128,24 +128,8 @@ class RoutedExperts(nn.Module):
         self._tables = None
 
     def address_tables(self, dtype, device):
-        """(gate_up addresses, down addresses, sizes, largest size, shared expert included?) as device arrays, or None when the
-        experts are not plain matrices of ``dtype`` (converted to a low-bit format); rebuilt when the weights moved.  A shared
-        expert that is a plain matrix too becomes the tables' last entry (the kernel runs it for every token)."""
-        def plain(mods):
-            return all(type(m) is nn.Linear and m.weight.dtype == dtype and m.weight.device == device and m.weight.is_contiguous() for m in mods)
-        experts = list(self.experts)
-        if not experts or not plain([m for e in experts for m in (e.gate_up, e.down)]):
-            return None
-        with_shared = self.shared is not None and plain([self.shared.gate_up, self.shared.down])
-        if with_shared:
-            experts.append(self.shared)
-        key = (device, dtype, with_shared) + tuple(m.weight.data_ptr() for e in (experts[0], experts[-1]) for m in (e.gate_up, e.down))
-        if self._tables is None or self._tables[0] != key:
-            def table(ws):
-                return torch.tensor([w.weight.data_ptr() for w in ws], dtype=torch.int64, device=device)
-            ffs = torch.tensor([e.ff for e in experts], dtype=torch.int32, device=device)
-            self._tables = (key, table([e.gate_up for e in experts]), table([e.down for e in experts]), ffs, max(e.ff for e in experts), with_shared)
-        return self._tables[1:]
+        """see ``experts.address_tables``"""
+        return experts.address_tables(self, dtype, device)
 
 
 class TokenSide(nn.Module):
@@ -255,22 +239,7 @@ class SerotarForCausalLM(PreTrainedModel, GenerationMixin):
             shared = mlp.shared(h) if (mlp.shared is not None and not with_shared) else None
             return ops.moe_small(h, idx, wgt, gate_up, down, ff_max, E, mlp.n_out, shared, ffs=ffs, always_on=with_shared)
         shared = mlp.shared(h) if mlp.shared is not None else None
-        # many tokens: the (token, choice) pairs sorted by expert on the device, one pair of matrix products per expert on its rows
-        # (the counts are read on the host: the one synchronisation of the layer)
-        counts, pos, token_of = ops.moe_sort(idx, mlp.n_out + 1)
-        counts = counts[:E].tolist()
-        rows = torch.empty(max(sum(counts), 1), h.shape[1], dtype=h.dtype, device=h.device)
-        off = 0
-        for e, cnt in enumerate(counts):
-            if cnt:
-                expert = mlp.experts[e]
-                a = ops.silu_mul(expert.gate_up(h.index_select(0, token_of[off:off + cnt])), expert.ff)
-                if type(expert.down) is nn.Linear:
-                    torch.mm(a, expert.down.weight.t(), out=rows[off:off + cnt])             # straight into the sorted rows
-                else:
-                    rows[off:off + cnt] = expert.down(a)
-                off += cnt
-        return ops.moe_combine(rows, pos, idx, wgt, h, shared, E, mlp.n_out)
+        return experts.sorted_experts(mlp, h, idx, wgt, mlp.n_out, lambda gu, expert: ops.silu_mul(gu, expert.ff), shared)
 
     def forward(self, input_ids: Optional[torch.LongTensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 position_ids=None, past_key_values=None, inputs_embeds=None, use_cache: Optional[bool] = None,
