@@ -1,7 +1,8 @@
 /* C ABI of libb200mixers.so: sequence-mixing and normalisation kernels for decoder layers that are not plain softmax
  * attention -- Dynamic-Tanh normalisation fused with the residual update, sliding-window attention with sigmoid weights,
- * short causal convolutions, the gated delta rule and gated linear attention recurrences, PolyNorm, gated RMS output norm,
- * soft-capped logits.  All pointers are device pointers; every function enqueues on `stream` and returns 0 or a cudaError_t.
+ * short causal convolutions, the gated delta rule, gated linear attention and RWKV-style recurrences, token shift, layer norm
+ * fused with the residual update, PolyNorm, gated RMS output norm, soft-capped logits, softmax attention over strided or latent
+ * caches (capped scores, sinks), routers and experts of mixtures of experts.  All pointers are device pointers; every function enqueues on `stream` and returns 0 or a cudaError_t.
  *
  * dtype: 0 = float, 1 = bfloat16, 2 = half: the type of activations AND of parameters (a model lives in one type).
  * Whatever the dtype, the residual stream, attention scores and weights, every normalisation and everything inside a
@@ -64,9 +65,30 @@ int mixers_gated_delta_rule(int dtype, const void* conv, int B, int S, int kv_he
 int mixers_gated_linear_attention(int dtype, const void* proj, int B, int S, int ld, int heads, int dim, int vdim, const void* z,
                                   float tau, float* state, int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
 
-/* out[n, out_col + h * vdim + c] = out_scale * o[n, h, c] / rms(o[n, h, :]) * w[c] * silu(gate[n, off_g + h * vdim + c]) */
+/* out[n, out_col + h * vdim + c] = out_scale * o[n, h, c] / rms(o[n, h, :]) * w[h * w_head_stride + c] * silu(gate[n, off_g + h * vdim + c])
+ * (w_head_stride 0: one weight vector [vdim] for every head; vdim: a vector per head, [heads * vdim]) */
 int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
-                          const void* w, float eps, void* out, int ld_out, int out_col, float out_scale, mixers_stream_t stream);
+                          const void* w, int w_head_stride, float eps, void* out, int ld_out, int out_col, float out_scale,
+                          mixers_stream_t stream);
+
+/* Token shift.  out[m, n, c] = h[n, c] + (h[n - 1, c] - h[n, c]) * mu[m, c], m < n_mix: h dtype [B, S, C], mu [n_mix, C], out
+ * [n_mix, B * S, C].  The token before a call's first one is tail [B, 1, C] (zeros before a sequence's first token); padding
+ * slots count as zeros and give zeros.  tail_next receives the last token's h (for S == 1 it may be `tail` itself).  pad may be
+ * null as in the recurrences. */
+int mixers_token_shift_mix(int dtype, const void* h, int B, int S, int C, const void* mu, int n_mix, const void* tail, void* tail_next,
+                           int slot0, const int32_t* pad, void* out, mixers_stream_t stream);
+
+/* RWKV-style recurrence with a decay per key channel and a bonus for the current token.  r, k, v: dtype, row n of each at
+ * ptr + n * ld, heads x dim channels (three tensors, or three column ranges of one); z [B, S, heads * dim]: decay logits, w =
+ * exp(-exp(z + w0)), w0 and u [heads * dim].  Per head:  o = (M + diag(u) k v^T)^T r;  M <- diag(w) M + k v^T.
+ * state: float [B, heads, dim, dim], updated in place; o: float [B, S, heads, dim]. */
+int mixers_wkv(int dtype, const void* r, const void* k, const void* v, int B, int S, int ld, int heads, int dim, const void* z,
+               const void* w0, const void* u, float* state, int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
+
+/* x += y_a + y_b (y_a dtype, y_b float; either may be null), then out = (x - mean) / sqrt(var + eps) * w over each row (out, w
+ * dtype; out may be null: only the update).  x: float [n_rows, width], updated in place. */
+int mixers_layer_norm_residual(int dtype, float* x, long n_rows, int width, const void* y_a, const float* y_b, const void* w, float eps,
+                               void* out, mixers_stream_t stream);
 
 /* out = a N(z) + b N(z^2) + c N(z^3) + e, N(v) = v / rms(v) over a row; coef = {a, b, c, e} */
 int mixers_poly_norm(int dtype, const void* z, long n_rows, int width, const void* coef, float eps, void* out, mixers_stream_t stream);
@@ -101,6 +123,10 @@ int mixers_xielu(int dtype, const void* z, long n, const void* pq, void* out, mi
 /* out[n, c] = silu(in[n, off_gate + c]) * in[n, off_up + c], c < cols; in: [n_rows, ld] */
 int mixers_silu_mul(int dtype, const void* in, long n_rows, int ld, int off_gate, int off_up, int cols, void* out, mixers_stream_t stream);
 
+/* out[n, c] = g' sigmoid(1.702 g') (u' + 1) with g' = min(in[n, off_gate + c], limit), u' = clamp(in[n, off_up + c], -limit, limit) */
+int mixers_clamped_glu(int dtype, const void* in, long n_rows, int ld, int off_gate, int off_up, int cols, float limit, void* out,
+                       mixers_stream_t stream);
+
 /* out[n, c] = gelu_tanh(g[n, c]) * table[ids[n], col0 + c], c < cols */
 int mixers_gelu_table_mul(int dtype, const void* g, long n_rows, int cols, const void* table, int ld_table, int col0, const int64_t* ids,
                           void* out, mixers_stream_t stream);
@@ -111,36 +137,57 @@ int mixers_latent_prepare(int dtype, const void* proj, int B, int S, int ld, int
                           int kv_rank, const void* c_w, float eps, void* cq_out, void* store, int cap, int held, int shift,
                           const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
 
+/* Queries, keys and values of new tokens from the columns of one projection output `proj` [B, S, ld], for attention that
+ * normalises a token's WHOLE query projection (heads * dim channels) and whole key projection (kv_heads * dim channels) at
+ * once: RMS norm with one weight per channel (q_w [heads * dim], k_w [kv_heads * dim]).  Queries go to q_out dtype
+ * [B * S, heads * dim]; keys and values into k_store [B, kv_heads, cap, dim] / v_store [.., vdim] at storage index held + t.
+ * With v_other (row n at v_other + n * ld_other, kv_heads * vdim channels: another layer's values of the same tokens) the
+ * stored value is (1 - blend[0]) v + blend[0] v_other.  Padding slots store zeros.  shift, dyn as above. */
+int mixers_wide_qkv_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
+                            int dim, int vdim, const void* q_w, const void* k_w, float eps, const void* v_other, long ld_other,
+                            const void* blend, void* q_out, void* k_store, void* v_store, int cap, int held, int shift,
+                            const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
+
 /* Causal softmax attention of S new tokens per row.  q: head h of token n at q + n * q_ld + h * q_hs.  Key (value) of storage
  * index j, row b, kv head g at k + b * k_bs + j * k_ps + g * k_hs (strides in elements).  The query at storage index c = held
  * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window.  Scores
- * (q . k) * scale and the softmax weights are 32-bit.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
+ * (q . k) * scale -- then softcap * tanh(score / softcap) if softcap > 0 -- and the softmax weights are 32-bit.  sink (dtype
+ * [heads], may be null): the denominator of head h's softmax also holds exp(sink[h]), which has no key and no value.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
  * allow_tensor_cores: 16-bit models may take the tensor-core kernels: for S >= 16 one block per 64 tokens of a head (head sizes
  * multiples of 16, <= 256); for S <= 16 and at least 4 query heads per kv head one pass over the keys for all heads of a
  * group, the keys split over blocks (dim a multiple of 16, <= 512; vdim 128, 256 or 512), which needs `ws`:
  * mixers_softmax_attention_workspace(...) floats (0: these sizes never take that kernel).  dyn as above. */
 int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                              long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
-                             int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
-                             const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream);
+                             int shift, const int32_t* pad, int window, float scale, float softcap, const void* sink, void* out,
+                             long ld_out, int out_col, const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream);
 long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int kv_heads, int dim, int vdim);
 
-/* Router of a mixture of experts.  z = router h (32-bit; router [n_out, width], h [n_rows, width] in dtype), s = softmax(z) over
- * all n_out outputs, choice = s + correction.  Outputs [g * n_out / groups, (g + 1) * n_out / groups) are group g; groups are
- * ranked by max(choice) over their members, the `keep` first groups stay eligible (every other output is out of the running,
- * whatever its sign), and the `top` eligible outputs of highest choice win.
- * idx_out int32 [n_rows, top] (n_out where nothing was left to choose), w_out float [n_rows, top] = s of the chosen. */
+/* Router of a mixture of experts.  z = router h (32-bit; router [n_out, width], h [n_rows, width] in dtype); s = softmax(z) over
+ * all n_out outputs (score_mode 0) or sigmoid(z) each (score_mode 1); choice = s + correction.  Outputs [g * n_out / groups,
+ * (g + 1) * n_out / groups) are group g; groups are ranked by the sum of their group_top largest choice scores, the `keep` first
+ * groups stay eligible (every other output is out of the running, whatever its sign), and the `top` eligible outputs of highest
+ * choice win (the lower index on a tie).  idx_out int32 [n_rows, top] (n_out where nothing was left to choose); w_out float
+ * [n_rows, top] = s of the chosen, divided by their sum + 1e-20 if renorm, times w_scale.  gate_row (dtype [width], may be null):
+ * gate_out[n] = sigmoid(gate_row . h[n]), the gate of an expert that every token runs. */
+int mixers_scored_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
+                         int groups, int keep, int top, int score_mode, int group_top, int renorm, float w_scale, const void* gate_row,
+                         float* gate_out, int32_t* idx_out, float* w_out, mixers_stream_t stream);
+/* the same with softmax scores, groups ranked by their best member, plain scores as weights */
 int mixers_grouped_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
                           int groups, int keep, int top, int32_t* idx_out, float* w_out, mixers_stream_t stream);
 
 /* The chosen experts of a few tokens without host work.  gate_up[e] / down[e]: addresses of expert e's [2 ff_e, width] (gate rows,
  * then up rows) and [width, ff_e] matrices in dtype; ffs[e] = ff_e (null: `ff` for all; `ff` is the largest).  always_on != 0:
- * table entry n_experts is an expert that every token runs with weight 1 (a shared expert).  act: scratch dtype [n_rows, top +
- * (always_on ? 1 : 0), ff].  y float [n_rows, width] = sum_k w_k * down_e (silu(gate_e h) * (up_e h)) for chosen e < n_experts,
- * w_k * h for n_experts <= e < n_out, + the always-on expert, + shared_out (dtype [n_rows, width], may be null). */
+ * table entry n_experts is an expert that every token runs (a shared expert) with weight always_w[n] (null: 1).  act: scratch dtype
+ * [n_rows, top + (always_on ? 1 : 0), ff].  The experts' activation A(g, u): act_kind 0 = silu(g) u; 1 = g' sigmoid(1.702 g')
+ * (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), L = `limit` for chosen experts and `limit_always` for the always-on one.
+ * y float [n_rows, width] = sum_k w_k * down_e A(gate_e h, up_e h) for chosen e < n_experts, w_k * h for n_experts <= e < n_out,
+ * + the always-on expert, + shared_out (dtype [n_rows, width], may be null). */
 int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
                      const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
-                     const void* shared_out, void* act, float* y, mixers_stream_t stream);
+                     const float* always_w, int act_kind, float limit, float limit_always, const void* shared_out, void* act, float* y,
+                     mixers_stream_t stream);
 
 /* Counting sort of n_pairs = n_rows * top (token, choice) pairs by chosen output idx[i] in [0, n_keys): counts[e] = pairs of e;
  * pos[i] = row of pair i among the sorted pairs; token_of[row] = i / top. */
@@ -148,9 +195,10 @@ int mixers_moe_sort(const int32_t* idx, long n_pairs, int top, int n_keys, int32
                     mixers_stream_t stream);
 
 /* y float [n_rows, width] = sum_k w[n, k] * rows[pos[n, k], :] for chosen e < n_experts, w * h[n, :] for identity experts,
- * + shared_out; rows: dtype [*, width], the experts' outputs on rows sorted by expert. */
+ * + shared_w[n] * shared_out (shared_w null: 1); rows: dtype [*, width], the experts' outputs on rows sorted by expert. */
 int mixers_moe_combine(int dtype, const void* rows, const int32_t* pos, const int32_t* idx, const float* wgt, const void* h,
-                       const void* shared_out, long n_rows, int width, int top, int n_experts, int n_out, float* y, mixers_stream_t stream);
+                       const void* shared_out, const float* shared_w, long n_rows, int width, int top, int n_experts, int n_out, float* y,
+                       mixers_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,5 +1,5 @@
 // Normalisations and other row-wise pieces: embedding gather into the 32-bit residual stream, Dynamic Tanh fused with the
-// residual update, gated RMS output norm of the recurrences, PolyNorm, soft-capped logits.  All of them are bound by memory
+// residual update, layer norm (weight only) fused with the residual update of a layer whose sublayers run side by side, gated RMS output norm of the recurrences, PolyNorm, soft-capped logits.  All of them are bound by memory
 // traffic: one pass over their rows, arithmetic in 32-bit floats.
 #include "mixers_common.cuh"
 
@@ -29,10 +29,86 @@ __global__ void dyt_residual_norm_kernel(float* __restrict__ x, long n_rows, int
     if (out) out[i] = from_f<T>(tanhf(to_f(pre_alpha[0]) * v) * to_f(pre_w[c]) + to_f(pre_b[c]));
 }
 
-// one warp per (row, head)
+// one block per row: x += (y_a + y_b) (either may be null; y_a in the model's type, y_b 32-bit), then out = layer norm of the new
+// x (mean removed, over the standard deviation, times w; no bias).  A row that fits LN_MAXC elements a thread is held in
+// registers (one round trip to memory), a wider one is read three times.  A prompt's many rows run in blocks of 128 threads
+// (many blocks per SM; the re-reads come from the caches); the few rows of a decoding step, which pay latency and nothing else,
+// get blocks of up to 1024 threads so that rows up to 8192 wide stay in registers.
+constexpr int LN_MAXC = 8, LN_FEW_ROWS = 64;
+template <int LN_THREADS>
+__device__ __forceinline__ float ln_block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_THREADS / 32; ++i) s += red[i];
+    return s;
+}
+
+template <typename T, int LN_THREADS>
+__global__ void __launch_bounds__(LN_THREADS) layer_norm_residual_kernel(float* __restrict__ x, int width, const T* __restrict__ y_a,
+                                                                       const float* __restrict__ y_b, const T* __restrict__ w, float eps,
+                                                                       T* __restrict__ out) {
+    __shared__ float red[LN_THREADS / 32];
+    const long base = (long)blockIdx.x * width;
+    const bool add = y_a || y_b;
+    if (width <= LN_MAXC * LN_THREADS) {
+        float v[LN_MAXC];
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LN_MAXC; ++k) {
+            const int c = threadIdx.x + k * LN_THREADS;
+            v[k] = 0.0f;
+            if (c < width) {
+                float a = y_a ? to_f(y_a[base + c]) : 0.0f;
+                if (y_b) a += y_b[base + c];
+                v[k] = add ? x[base + c] + a : x[base + c];
+                if (add) x[base + c] = v[k];
+                sum += v[k];
+            }
+        }
+        if (!out) return;
+        const float mean = ln_block_sum<LN_THREADS>(sum, red) / (float)width;
+        float sq = 0.0f;
+#pragma unroll
+        for (int k = 0; k < LN_MAXC; ++k) {
+            const int c = threadIdx.x + k * LN_THREADS;
+            if (c < width) { v[k] -= mean; sq += v[k] * v[k]; }
+        }
+        const float inv = 1.0f / sqrtf(ln_block_sum<LN_THREADS>(sq, red) / (float)width + eps);
+#pragma unroll
+        for (int k = 0; k < LN_MAXC; ++k) {
+            const int c = threadIdx.x + k * LN_THREADS;
+            if (c < width) out[base + c] = from_f<T>(v[k] * inv * to_f(w[c]));
+        }
+        return;
+    }
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < width; c += LN_THREADS) {
+        float v = x[base + c];
+        if (add) {
+            float a = y_a ? to_f(y_a[base + c]) : 0.0f;
+            if (y_b) a += y_b[base + c];
+            v += a;
+            x[base + c] = v;
+        }
+        sum += v;
+    }
+    if (!out) return;
+    const float mean = ln_block_sum<LN_THREADS>(sum, red) / (float)width;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += LN_THREADS) { const float d = x[base + c] - mean; sq += d * d; }
+    const float inv = 1.0f / sqrtf(ln_block_sum<LN_THREADS>(sq, red) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += LN_THREADS) out[base + c] = from_f<T>((x[base + c] - mean) * inv * to_f(w[c]));
+}
+
+// one warp per (row, head); w_head_stride: 0 = one weight vector [vdim] for every head, vdim = a vector per head [heads * vdim]
 template <typename T>
 __global__ void gated_rms_norm_kernel(const float* __restrict__ o, long n_rows, int heads, int vdim, const T* __restrict__ gate, int ld_gate,
-                                      int off_g, const T* __restrict__ w, float eps, T* __restrict__ out, int ld_out, int out_col, float out_scale) {
+                                      int off_g, const T* __restrict__ w, int w_head_stride, float eps, T* __restrict__ out, int ld_out, int out_col,
+                                      float out_scale) {
     long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     if (warp >= n_rows * heads) return;
@@ -45,6 +121,7 @@ __global__ void gated_rms_norm_kernel(const float* __restrict__ o, long n_rows, 
     float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
     const T* g = gate + n * (long)ld_gate + off_g + h * vdim;
     T* dst = out + n * (long)ld_out + out_col + h * vdim;
+    w += (long)h * w_head_stride;
     for (int c = lane; c < vdim; c += 32)
         dst[c] = from_f<T>(src[c] * inv * to_f(w[c]) * silu_f(to_f(g[c])) * out_scale);
 }
@@ -107,13 +184,32 @@ extern "C" int mixers_dyt_residual_norm(int dtype, float* x, long n_rows, int wi
     return mixers_status();
 }
 
+extern "C" int mixers_layer_norm_residual(int dtype, float* x, long n_rows, int width, const void* y_a, const float* y_b, const void* w, float eps,
+                                          void* out, mixers_stream_t stream) {
+    if (n_rows <= 0 || (!y_a && !y_b && !out)) return 0;
+    if (out && !w) return (int)cudaErrorInvalidValue;
+    int threads = 128;
+    if (n_rows <= LN_FEW_ROWS)
+        while (threads < 1024 && threads * LN_MAXC < width) threads <<= 1;
+#define LN_LAUNCH(TH) MIXERS_DISPATCH(dtype, layer_norm_residual_kernel<T, TH><<<(unsigned)n_rows, TH, 0, (cudaStream_t)stream>>>( \
+        x, width, (const T*)y_a, y_b, (const T*)w, eps, (T*)out))
+    if (threads == 128) LN_LAUNCH(128);
+    else if (threads == 256) LN_LAUNCH(256);
+    else if (threads == 512) LN_LAUNCH(512);
+    else LN_LAUNCH(1024);
+#undef LN_LAUNCH
+    return mixers_status();
+}
+
 extern "C" int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
-                                     const void* w, float eps, void* out, int ld_out, int out_col, float out_scale, mixers_stream_t stream) {
+                                     const void* w, int w_head_stride, float eps, void* out, int ld_out, int out_col, float out_scale,
+                                     mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
     long warps = n_rows * heads;
     int blocks = (int)((warps + 3) / 4);
     MIXERS_DISPATCH(dtype, gated_rms_norm_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(o, n_rows, heads, vdim, (const T*)gate, ld_gate, off_g,
-                                                                                                (const T*)w, eps, (T*)out, ld_out, out_col, out_scale));
+                                                                                                (const T*)w, w_head_stride, eps, (T*)out, ld_out, out_col,
+                                                                                                out_scale));
     return mixers_status();
 }
 

@@ -3,6 +3,7 @@
 // Both recurrences act on every COLUMN of the state independently (a column = one value channel): with M [dim, vdim],
 //   gated delta rule:        M <- g M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q
 //   gated linear attention:  M <- diag(alpha) M + k v^T;       o = M^T q
+//   wkv (RWKV-style):        o = (M + diag(u) k v^T)^T r;      M <- diag(w) M + k v^T     (w = exp(-exp(z + w0)) per key channel)
 // column j only needs k, q, the token's scalars and v_j.  So a column is owned by LPC lanes of a warp (LPC a power of two), each
 // holding R rows of it in registers for the whole call; tokens are taken in order.  Half of the block's warps own columns; the
 // other half stage the NEXT 16 tokens meanwhile in the second of two shared-memory buffers: their k / q (/ alpha) rows, scalars
@@ -10,6 +11,8 @@
 // For the delta rule both dot products are taken on the state BEFORE the token's update,
 //   a = M_old^T k,  c = M_old^T q:   u = beta (v - g a),   o = g c + (k . q) u,   M <- g M_old + k u^T,
 // which is the same arithmetic reordered so that one round of shuffles serves both.
+// The wkv output reads the state BEFORE the token's update plus a bonus for the token itself: o = M_old^T r + (sum_i r_i u_i k_i) v;
+// the bonus factor is a scalar per token and head, formed while the token is staged.
 #include "mixers_common.cuh"
 
 // one block row per token (blockIdx.x), channels across the block and blockIdx.y: no index division in the loop
@@ -38,6 +41,26 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S,
         for (int r = 0; r < taps - 1; ++r) tail_next[((long)b * tl + r) * C + c] = from_f<T>(input(S - (taps - 1) + r));
 }
 
+// Token shift: out[m, n, c] = h[n, c] + (h[n - 1, c] - h[n, c]) * mu[m, c] for each of n_mix mixing vectors; the token before a
+// call's first one comes from tail [B, 1, C] (zeros before a sequence's first token), padding slots count as zeros and give
+// zeros.  tail_next receives the last token's h (it may be `tail` itself when S == 1: the thread that reads a channel writes it).
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ h, int B, int S, int C, const T* __restrict__ mu, int n_mix, const T* __restrict__ tail,
+                                       T* __restrict__ tail_next, int slot0, const int32_t* __restrict__ pad, T* __restrict__ out) {
+    const int n = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int b = n / S, t = n - b * S;
+    int first = pad ? pad[b] - slot0 : 0;
+    if (first < 0) first = 0;
+    const long total = (long)B * S * C;
+    const float cur = t < first ? 0.0f : to_f(h[(long)n * C + c]);
+    const float before = t == 0 ? to_f(tail[(long)b * C + c]) : (t - 1 < first ? 0.0f : to_f(h[(long)(n - 1) * C + c]));
+    for (int m = 0; m < n_mix; ++m)
+        out[m * total + (long)n * C + c] = from_f<T>(t < first ? 0.0f : cur + (before - cur) * to_f(mu[(long)m * C + c]));
+    if (t == S - 1) tail_next[(long)b * C + c] = from_f<T>(cur);
+}
+
 constexpr int REC_CONSUMERS = 128;                          // threads that own state columns (4 warps)
 constexpr int REC_PRODUCERS = 128;                          // threads that stage the next tokens meanwhile (4 warps)
 constexpr int REC_THREADS = REC_CONSUMERS + REC_PRODUCERS;
@@ -47,14 +70,17 @@ constexpr int REC_TC = REC_TPW * (REC_PRODUCERS / 32);      // tokens per stage 
 struct RecArgs {
     const void* src;        // delta: conv output [B, S, C]; gla: projection [B, S, ld]
     int ld_src;
-    int off_q, off_k, off_v;   // column offsets of head 0 inside a row of src
+    long off_q, off_k, off_v;  // offsets (elements) of head 0 from the start of a row of src: columns of one projection, or whole
+                            // tensors apart when q, k and v are separate [B * S, heads * dim] outputs that follow one another
     int q_heads;            // heads of q / k (delta: kv_heads; gla: heads)
     const void* proj;       // delta: the projection that holds beta / decay logits
     int ld_proj, off_b, off_a;
     const void* A_log;
     const void* dt_bias;
-    const void* z;          // gla: decay logits [B, S, heads * dim]
+    const void* z;          // gla, wkv: decay logits [B, S, heads * dim]
     float inv_tau;
+    const void* w0;         // wkv: added to the decay logits [heads * dim]
+    const void* u;          // wkv: the current token's bonus [heads * dim]
     int B, S, heads, dim, vdim, slot0;
     const int32_t* pad;
     float* state;
@@ -67,9 +93,9 @@ template <int MODE>
 struct RecStage {
     float *k, *q, *a, *v, *sc;
     __device__ RecStage(float* base, int tc, int dp, int cols_blk) {
-        k = base; q = k + tc * dp; a = q + tc * dp; v = a + (MODE == 1 ? tc * dp : 0); sc = v + tc * cols_blk;
+        k = base; q = k + tc * dp; a = q + tc * dp; v = a + (MODE != 0 ? tc * dp : 0); sc = v + tc * cols_blk;
     }
-    static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((MODE == 1 ? 3 : 2) * dp + cols_blk + 4); }
+    static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((MODE != 0 ? 3 : 2) * dp + cols_blk + 4); }
 };
 
 // producers: tokens t0 .. t0 + nt - 1 of the call into one stage.  A warp takes up to REC_TPW tokens at once, and EVERY global
@@ -109,18 +135,26 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
 #pragma unroll
         for (int j = 0; j < REC_TPW; ++j) sq[j] = sk[j] = skq[j] = 0.0f;
         for (int blk = 0; blk < dp; blk += 128) {
-            float qv[REC_TPW][4], kv[REC_TPW][4], zv[REC_TPW][4];
+            float qv[REC_TPW][4], kv[REC_TPW][4], zv[REC_TPW][4], w0v[4], uv[4];
+            if (MODE == 2) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = blk + lane + 32 * e;
+                    w0v[e] = i < dim ? to_f(((const T*)a.w0)[h * dim + i]) : 0.0f;
+                    uv[e] = i < dim ? to_f(((const T*)a.u)[h * dim + i]) : 0.0f;
+                }
+            }
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) {
                 const T* row = src + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * a.ld_src;
-                const T* zr = MODE == 1 ? (const T*)a.z + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * ((long)a.heads * dim) + h * dim : nullptr;
+                const T* zr = MODE != 0 ? (const T*)a.z + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * ((long)a.heads * dim) + h * dim : nullptr;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = blk + lane + 32 * e;
                     const bool ok = j < cnt && i < dim;
                     qv[j][e] = ok ? to_f(row[a.off_q + qh * dim + i]) : 0.0f;
                     kv[j][e] = ok ? to_f(row[a.off_k + qh * dim + i]) : 0.0f;
-                    if (MODE == 1) zv[j][e] = ok ? to_f(zr[i]) : 0.0f;
+                    if (MODE != 0) zv[j][e] = ok ? to_f(zr[i]) : 0.0f;
                 }
             }
 #pragma unroll
@@ -133,11 +167,15 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
                             if (MODE == 1) {
                                 st.a[(tt0 + j) * dp + i] = i < dim ? expf(log_sigmoid_f(zv[j][e]) * a.inv_tau) : 1.0f;
                                 st.q[(tt0 + j) * dp + i] = qv[j][e] * q_scale;
+                            } else if (MODE == 2) {
+                                st.a[(tt0 + j) * dp + i] = i < dim ? expf(-expf(zv[j][e] + w0v[e])) : 1.0f;
+                                st.q[(tt0 + j) * dp + i] = qv[j][e];
+                                skq[j] += qv[j][e] * uv[e] * kv[j][e];
                             } else {
                                 st.q[(tt0 + j) * dp + i] = qv[j][e];
+                                sq[j] += qv[j][e] * qv[j][e]; sk[j] += kv[j][e] * kv[j][e]; skq[j] += qv[j][e] * kv[j][e];
                             }
                             st.k[(tt0 + j) * dp + i] = kv[j][e];
-                            sq[j] += qv[j][e] * qv[j][e]; sk[j] += kv[j][e] * kv[j][e]; skq[j] += qv[j][e] * kv[j][e];
                         }
                     }
                 }
@@ -161,6 +199,12 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
                 st.sc[(tt0 + lane) * 4 + 1] = sigmoid_f(lb);
                 st.sc[(tt0 + lane) * 4 + 2] = my_kq * my_nq * my_nk;
             }
+        }
+        if (MODE == 2) {
+            float mine = 0.0f;
+#pragma unroll
+            for (int j = 0; j < REC_TPW; ++j) { const float tot = warp_sum(skq[j]); if (lane == j) mine = tot; }
+            if (lane < cnt) st.sc[(tt0 + lane) * 4 + 2] = mine;
         }
     }
 #pragma unroll
@@ -249,13 +293,21 @@ __global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs 
                     o = g * cqs + kq * u;
 #pragma unroll
                     for (int r = 0; r < R; ++r) M[r] += kr[r] * u;
-                } else {
+                } else if (MODE == 1) {
                     const float* aa = st.a + tt * dp + sub;
                     float op[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                     for (int r = 0; r < R; ++r) { M[r] = aa[r * lpc] * M[r] + kr[r] * v; op[r & 3] += M[r] * qr[r]; }
                     o = (op[0] + op[1]) + (op[2] + op[3]);
                     for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                } else {
+                    const float* aa = st.a + tt * dp + sub;
+                    float op[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { op[r & 3] += M[r] * qr[r]; M[r] = aa[r * lpc] * M[r] + kr[r] * v; }
+                    o = (op[0] + op[1]) + (op[2] + op[3]);
+                    for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                    o += st.sc[tt * 4 + 2] * v;
                 }
                 if (sub == 0 && col_ok) obase[(long)(t0 + tt) * a.heads * vdim + col] = o;
             }
@@ -283,9 +335,9 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
     const int cols_blk = REC_FEW_THREADS / lpc;
     float* kbuf = sh;                                        // [tc][dp]
     float* qbuf = kbuf + tc * dp;                            // [tc][dp]
-    float* abuf = qbuf + tc * dp;                            // [tc][dp] (gla only)
-    float* vbuf = abuf + (MODE == 1 ? tc * dp : 0);          // [tc][cols_blk]
-    float* sc = vbuf + tc * cols_blk;                        // [tc][4]: g, beta, k.q
+    float* abuf = qbuf + tc * dp;                            // [tc][dp] (gla, wkv)
+    float* vbuf = abuf + (MODE != 0 ? tc * dp : 0);          // [tc][cols_blk]
+    float* sc = vbuf + tc * cols_blk;                        // [tc][4]: g, beta, k.q (wkv: [2] = sum r u k)
     const int b = blockIdx.z, h = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int sub = tid % lpc;
@@ -339,12 +391,23 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
                     sc[tt * 4 + 1] = beta;
                     sc[tt * 4 + 2] = skq * nq * nk;
                 }
-            } else {
+            } else if (MODE == 1) {
                 const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
                 for (int i = lane; i < dp; i += 32) {
                     qbuf[tt * dp + i] *= q_scale;
                     abuf[tt * dp + i] = i < dim ? expf(log_sigmoid_f(to_f(zr[i])) * a.inv_tau) : 1.0f;
                 }
+            } else {
+                const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
+                const T* w0 = (const T*)a.w0 + h * dim;
+                const T* uu = (const T*)a.u + h * dim;
+                float ruk = 0.0f;
+                for (int i = lane; i < dp; i += 32) {
+                    abuf[tt * dp + i] = i < dim ? expf(-expf(to_f(zr[i]) + to_f(w0[i]))) : 1.0f;
+                    if (i < dim) ruk += qbuf[tt * dp + i] * to_f(uu[i]) * kbuf[tt * dp + i];
+                }
+                ruk = warp_sum(ruk);
+                if (lane == 0) sc[tt * 4 + 2] = ruk;
             }
         }
         for (int i = tid; i < nt * cols_blk; i += REC_FEW_THREADS) {
@@ -369,12 +432,19 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
                 o = g * cq + kq * u;
 #pragma unroll
                 for (int r = 0; r < R; ++r) M[r] = g * M[r] + kk[r * lpc] * u;
-            } else {
+            } else if (MODE == 1) {
                 const float* aa = abuf + tt * dp + sub;
                 o = 0.0f;
 #pragma unroll
                 for (int r = 0; r < R; ++r) { M[r] = aa[r * lpc] * M[r] + kk[r * lpc] * v; o += M[r] * qq[r * lpc]; }
                 for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+            } else {
+                const float* aa = abuf + tt * dp + sub;
+                o = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { o += M[r] * qq[r * lpc]; M[r] = aa[r * lpc] * M[r] + kk[r * lpc] * v; }
+                for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                o += sc[tt * 4 + 2] * v;
             }
             if (sub == 0 && col_ok) obase[(long)(t0 + tt) * a.heads * vdim + col] = o;
         }
@@ -397,7 +467,7 @@ static int launch_recurrence_few(RecArgs a, cudaStream_t stream) {
     while (lpc < need) lpc <<= 1;
     if (lpc > 32) return (int)cudaErrorInvalidValue;
     int dp = r * lpc, cols_blk = REC_FEW_THREADS / lpc;
-    int arrays = MODE == 1 ? 3 : 2;
+    int arrays = MODE != 0 ? 3 : 2;
     int tc = a.S < REC_TC ? a.S : REC_TC;
     auto bytes = [&](int n) { return (size_t)n * (arrays * dp + cols_blk + 4) * sizeof(float); };
     while (tc > 1 && bytes(tc) > 40 * 1024) tc >>= 1;
@@ -445,6 +515,16 @@ extern "C" int mixers_short_conv_silu(int dtype, const void* proj, int B, int S,
     return mixers_status();
 }
 
+extern "C" int mixers_token_shift_mix(int dtype, const void* h, int B, int S, int C, const void* mu, int n_mix, const void* tail, void* tail_next,
+                                      int slot0, const int32_t* pad, void* out, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
+    dim3 blocks((unsigned)((long)B * S), (unsigned)((C + threads - 1) / threads));
+    MIXERS_DISPATCH(dtype, token_shift_mix_kernel<T><<<blocks, threads, 0, (cudaStream_t)stream>>>((const T*)h, B, S, C, (const T*)mu, n_mix, (const T*)tail,
+                                                                                                 (T*)tail_next, slot0, pad, (T*)out));
+    return mixers_status();
+}
+
 extern "C" int mixers_gated_delta_rule(int dtype, const void* conv, int B, int S, int kv_heads, int heads, int dim, int vdim,
                                        const void* proj, int ld, int off_b, int off_a, const void* A_log, const void* dt_bias, float* state,
                                        int slot0, const int32_t* pad, float* o, mixers_stream_t stream) {
@@ -467,5 +547,18 @@ extern "C" int mixers_gated_linear_attention(int dtype, const void* proj, int B,
     a.z = z; a.inv_tau = 1.0f / tau;
     a.B = B; a.S = S; a.heads = heads; a.dim = dim; a.vdim = vdim; a.slot0 = slot0; a.pad = pad; a.state = state; a.o = o;
     MIXERS_DISPATCH(dtype, return (launch_recurrence<T, 1>(a, (cudaStream_t)stream)));
+    return 0;
+}
+
+extern "C" int mixers_wkv(int dtype, const void* r, const void* k, const void* v, int B, int S, int ld, int heads, int dim, const void* z,
+                          const void* w0, const void* u, float* state, int slot0, const int32_t* pad, float* o, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    const long esz = dtype == 0 ? 4 : 2;
+    RecArgs a = {};
+    a.src = r; a.ld_src = ld; a.off_q = 0;
+    a.off_k = (long)(((const char*)k - (const char*)r) / esz); a.off_v = (long)(((const char*)v - (const char*)r) / esz);
+    a.q_heads = heads; a.z = z; a.w0 = w0; a.u = u;
+    a.B = B; a.S = S; a.heads = heads; a.dim = dim; a.vdim = dim; a.slot0 = slot0; a.pad = pad; a.state = state; a.o = o;
+    MIXERS_DISPATCH(dtype, return (launch_recurrence<T, 2>(a, (cudaStream_t)stream)));
     return 0;
 }

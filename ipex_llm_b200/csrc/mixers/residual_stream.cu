@@ -173,6 +173,19 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, long n_rows, int ld, i
     }
 }
 
+// out[n, c] = g' sigmoid(1.702 g') (u' + 1), g' = min(in[n, off_gate + c], limit), u' = clamp(in[n, off_up + c], -limit, limit)
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ in, long n_rows, int ld, int off_gate, int off_up, int cols, float limit, T* __restrict__ out) {
+    const long total = n_rows * cols;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long n = i / cols;
+        const int c = (int)(i - n * cols);
+        const float g = fminf(to_f(in[n * ld + off_gate + c]), limit);
+        const float u = fminf(fmaxf(to_f(in[n * ld + off_up + c]), -limit), limit);
+        out[i] = from_f<T>(g * sigmoid_f(1.702f * g) * (u + 1.0f));
+    }
+}
+
 // out[n, c] = gelu_tanh(g[n, c]) * table[ids[n], col0 + c]
 template <typename T>
 __global__ void gelu_table_mul_kernel(const T* __restrict__ g, long n_rows, int cols, const T* __restrict__ table, int ld_table, int col0,
@@ -257,5 +270,13 @@ extern "C" int mixers_gelu_table_mul(int dtype, const void* g, long n_rows, int 
     if (n_rows <= 0 || cols <= 0) return 0;
     MIXERS_DISPATCH(dtype, gelu_table_mul_kernel<T><<<grid_for(n_rows * cols), 256, 0, (cudaStream_t)stream>>>(
         (const T*)g, n_rows, cols, (const T*)table, ld_table, col0, ids, (T*)out));
+    return mixers_status();
+}
+
+extern "C" int mixers_clamped_glu(int dtype, const void* in, long n_rows, int ld, int off_gate, int off_up, int cols, float limit, void* out,
+                                  mixers_stream_t stream) {
+    if (n_rows <= 0 || cols <= 0) return 0;
+    MIXERS_DISPATCH(dtype, clamped_glu_kernel<T><<<grid_for(n_rows * cols), 256, 0, (cudaStream_t)stream>>>((const T*)in, n_rows, ld, off_gate, off_up, cols,
+                                                                                                          limit, (T*)out));
     return mixers_status();
 }

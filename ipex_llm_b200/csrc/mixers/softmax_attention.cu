@@ -5,7 +5,11 @@
 //     [batch, position, kv head, channel] tensors given by three strides each, so the same kernels serve keys / values
 //     expanded from the latent (one row per head) and the latent cache itself read as one shared key = value head of
 //     kv_rank channels (the "absorbed" form: the query carries the key expansion, the value expansion follows the sum).
-//   An optional window limits how far back a query looks (0 = every earlier position).
+//   An optional window limits how far back a query looks (0 = every earlier position); scores may be soft-capped
+//   (cap * tanh(score / cap)) and the softmax's denominator may hold a per-head sink exp(sink_h) that has no key and no value.
+//   wide_qkv_prepare: RMS norm over a token's WHOLE query projection and whole key projection (all heads at once, one weight per
+//     channel), values optionally blended with another layer's values of the same token; keys and values are appended to the
+//     cache.
 #include "mixers_common.cuh"
 #include <math.h>
 
@@ -60,6 +64,76 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(
     }
 }
 
+// one block per (token, segment): 0 = queries (norm over heads * dim channels -> q_out), 1 = keys (norm over kv_heads * dim
+// channels -> cache), 2 = values ((1 - blend) v + blend v_other when v_other is given -> cache).  Padding slots store zeros.
+// a segment that fits QP_MAXC elements a thread is held in registers; a prompt's many tokens run in blocks of 128 threads, the few
+// tokens of a decoding step in blocks of up to 1024 so that projections up to 8192 wide take one round trip to memory
+constexpr int QP_MAXC = 8, QP_FEW_TOKENS = 64;
+template <typename T, int QP_THREADS>
+__global__ void __launch_bounds__(QP_THREADS) wide_qkv_prepare_kernel(
+        const T* __restrict__ proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads, int dim, int vdim,
+        const T* __restrict__ q_w, const T* __restrict__ k_w, float eps, const T* __restrict__ v_other, long ld_other, const T* __restrict__ blend,
+        T* __restrict__ q_out, T* __restrict__ k_store, T* __restrict__ v_store, int cap, int held, int shift, const int32_t* __restrict__ pad,
+        const int32_t* __restrict__ dyn) {
+    __shared__ float red[QP_THREADS / 32];
+    if (dyn) held = dyn[0];
+    const long n = blockIdx.x / 3;
+    const int seg = blockIdx.x - 3 * n;
+    const int b = (int)(n / S), t = (int)(n - (long)b * S);
+    const bool real = held + t + shift - pad[b] >= 0;
+    const T* row = proj + n * (long)ld;
+    if (seg == 2) {
+        const int width = kv_heads * vdim;
+        const float lam = v_other ? to_f(blend[0]) : 0.0f;
+        for (int c = threadIdx.x; c < width; c += QP_THREADS) {
+            float v = to_f(row[off_v + c]);
+            if (v_other) v = (1.0f - lam) * v + lam * to_f(v_other[n * ld_other + c]);
+            const int g = c / vdim;
+            v_store[(((long)b * kv_heads + g) * cap + held + t) * vdim + (c - g * vdim)] = from_f<T>(real ? v : 0.0f);
+        }
+        return;
+    }
+    const int hd = seg ? kv_heads : heads;
+    const int width = hd * dim;
+    const T* src = row + (seg ? off_k : off_q);
+    const T* w = seg ? k_w : q_w;
+    const bool cached = width <= QP_MAXC * QP_THREADS;
+    float sv[QP_MAXC];
+    float ss = 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int k = 0; k < QP_MAXC; ++k) {
+            const int c = threadIdx.x + k * QP_THREADS;
+            sv[k] = c < width ? to_f(src[c]) : 0.0f;
+            ss += sv[k] * sv[k];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += QP_THREADS) { float v = to_f(src[c]); ss += v * v; }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < QP_THREADS / 32; ++i) ss += red[i];
+    const float inv = real ? 1.0f / sqrtf(ss / (float)width + eps) : 0.0f;
+    auto put = [&](int c, float v) {
+        const float y = v * inv * to_f(w[c]);
+        if (seg == 0) { q_out[n * (long)width + c] = from_f<T>(y); return; }
+        const int g = c / dim;
+        k_store[(((long)b * kv_heads + g) * cap + held + t) * dim + (c - g * dim)] = from_f<T>(y);
+    };
+    if (cached) {
+#pragma unroll
+        for (int k = 0; k < QP_MAXC; ++k) {
+            const int c = threadIdx.x + k * QP_THREADS;
+            if (c < width) put(c, sv[k]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += QP_THREADS) put(c, to_f(src[c]));
+    }
+}
+
 // ---- the general kernel: any sizes and strides, any dtype, 32-bit arithmetic throughout (float32 models, decoding, short
 // portions).  A block of SA_WARPS warps per (token, query head); the warps take the visible keys in turns of 32, each with its
 // own running maximum, sum and weighted values; the warps' partial results are merged in shared memory in warp order.
@@ -78,7 +152,7 @@ template <typename T>
 __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
-        float scale, T* __restrict__ out, long ld_out, int out_col, const int32_t* __restrict__ dyn, int aligned) {
+        float scale, float softcap, const T* __restrict__ sink, T* __restrict__ out, long ld_out, int out_col, const int32_t* __restrict__ dyn, int aligned) {
     extern __shared__ __align__(16) float sa_sh[];          // q [dim rounded up to 4], warp maxima, warp sums, partial values
     const int dim4 = (dim + 3) & ~3;
     float* qs = sa_sh;
@@ -114,7 +188,11 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
         for (int i = 0; i < SA_VCOLS; ++i) acc[i] = 0.0f;
         for (int j0 = lo + 32 * wid; j0 <= c; j0 += 32 * SA_WARPS) {
             const int j = j0 + lane;
-            const float s = j <= c ? dot_strided(qs, kbase + j * k_ps, dim, aligned != 0) * scale : -INFINITY;
+            float s = -INFINITY;
+            if (j <= c) {
+                s = dot_strided(qs, kbase + j * k_ps, dim, aligned != 0) * scale;
+                if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
+            }
             const float m_new = fmaxf(m, warp_max(s));      // finite: key j0 is visible
             const float corr = expf(m - m_new);             // 0 on the first turn (m = -inf)
             const float p = j <= c ? expf(s - m_new) : 0.0f;
@@ -143,6 +221,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
         float f[SA_WARPS], total = 0.0f;
 #pragma unroll
         for (int w = 0; w < SA_WARPS; ++w) { f[w] = wm[w] == -INFINITY ? 0.0f : expf(wm[w] - big); total += wl[w] * f[w]; }
+        if (sink) total += expf(to_f(sink[h]) - big);       // a sink far above every score: the sum overflows and the output is 0, its limit
         for (int e = threadIdx.x; e < SA_VCOLS * 32; e += blockDim.x) {
             const int col = col0 + e;                       // e = i * 32 + lane, column = col0 + lane + 32 i
             if (col < vdim) {
@@ -188,11 +267,17 @@ template <> struct SaMma<__half> {
 
 constexpr int SA_ROWS = 64, SA_KEYS = 32;
 
+// cap * tanh(s / cap) with the hardware exponential: tanh(y) = 1 - 2 / (e^2y + 1), exact at both ends (cap <= 0: s itself)
+__device__ __forceinline__ float fast_cap(float s, float cap, float inv_cap) {
+    if (cap <= 0.0f) return s;
+    return cap * (1.0f - __fdividef(2.0f, __expf(2.0f * s * inv_cap) + 1.0f));
+}
+
 template <typename T, int KDMAX, int NDMAX>                // dim <= 16 KDMAX, vdim <= 8 NDMAX; both multiples of 16
 __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
-        float scale, T* __restrict__ out, long ld_out, int out_col) {
+        float scale, float softcap, const T* __restrict__ sink, T* __restrict__ out, long ld_out, int out_col) {
     extern __shared__ __align__(16) unsigned char sa_tc_sh[];
     const int kstride = dim + 8, vstride = vdim + 8;        // elements
     T* Ks = reinterpret_cast<T*>(sa_tc_sh);                 // two stages of [SA_KEYS][kstride] keys + [SA_KEYS][vstride] values
@@ -246,6 +331,8 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
     const T* kbase = k + b * k_bs + g * k_hs;
     const T* vbase = v + b * v_bs + g * v_hs;
     const int kchunks = dim >> 3, vchunks = vdim >> 3;      // 16-byte pieces per row
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
+    const float sinkv = sink ? to_f(sink[h]) : -INFINITY;
 
     // two stages of K / V tiles: the next tile's copies (cp.async, 16 bytes each) are in flight while this one is multiplied
     auto load_tile = [&](int stage, int jt) {
@@ -301,7 +388,7 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
                 for (int i = 0; i < 4; ++i) {
                     const int j = jt + nt * 8 + 2 * tq + (i & 1);
                     const int r = i >> 1;
-                    const float s = (j >= row_lo[r] && j <= row_c[r]) ? sc[nt][i] * scale : -INFINITY;
+                    const float s = (j >= row_lo[r] && j <= row_c[r]) ? fast_cap(sc[nt][i] * scale, softcap, inv_cap) : -INFINITY;
                     sc[nt][i] = s;
                     tmax[r] = fmaxf(tmax[r], s);
                 }
@@ -365,6 +452,7 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
         float l = l_run[i];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (l > 0.0f && sink) l += __expf(sinkv - m_run[i]);                 // overflow = a sink far above every score: output 0
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         if (tr[i] < S) {
             T* dst = out + ((long)b * S + tr[i]) * ld_out + out_col + (long)h * vdim + 2 * tq;
@@ -392,7 +480,7 @@ template <typename T, int NT, bool SAME>                   // vdim = 64 NT (each
 __global__ void __launch_bounds__(256) shared_head_attention_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
         long v_hs, int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* __restrict__ pad, int window, float scale,
-        float* __restrict__ ws, int splits, int tiles, const int32_t* __restrict__ dyn) {
+        float softcap, float* __restrict__ ws, int splits, int tiles, const int32_t* __restrict__ dyn) {
     constexpr int vdim = 64 * NT;
     extern __shared__ __align__(16) unsigned char sh_raw[];
     const int kstride = dim + 8, vstride = vdim + 8;
@@ -446,6 +534,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
     const T* kbase = k + b * k_bs + g * k_hs;
     const T* vbase = v + b * v_bs + g * v_hs;
     const int kchunks = dim >> 3, vchunks = vdim >> 3, kdn = dim >> 4;
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
 
     // two stages of key (and value) tiles: the next tile's copies (cp.async, 16 bytes each) fly while this one is multiplied
     auto load_tile = [&](int stage, int jt) {
@@ -507,8 +596,8 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
             for (int r = 0; r < 2; ++r) {
                 float2 out;
                 const int j = jt + wid * 8 + 2 * tq;
-                out.x = (j >= my_lo[r] && j <= my_c[r] && j <= j_hi) ? sc[2 * r] * scale : -INFINITY;
-                out.y = (j + 1 >= my_lo[r] && j + 1 <= my_c[r] && j + 1 <= j_hi) ? sc[2 * r + 1] * scale : -INFINITY;
+                out.x = (j >= my_lo[r] && j <= my_c[r] && j <= j_hi) ? fast_cap(sc[2 * r] * scale, softcap, inv_cap) : -INFINITY;
+                out.y = (j + 1 >= my_lo[r] && j + 1 <= my_c[r] && j + 1 <= j_hi) ? fast_cap(sc[2 * r + 1] * scale, softcap, inv_cap) : -INFINITY;
                 *reinterpret_cast<float2*>(Ss + (gr + 8 * r) * SH_SSTRIDE + wid * 8 + 2 * tq) = out;
             }
         }
@@ -591,7 +680,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
 // maxima into factors; then every thread owns two neighbouring columns and reads them from all ranges (independent loads).
 template <typename T>
 __global__ void __launch_bounds__(256) shared_head_merge_kernel(const float* __restrict__ ws, int S, int heads, int kv_heads, int vdim, int splits,
-                                                                int tiles, T* __restrict__ out, long ld_out, int out_col) {
+                                                                int tiles, const T* __restrict__ sink, T* __restrict__ out, long ld_out, int out_col) {
     __shared__ float factor[SH_MAX_SPLITS];
     __shared__ float inv_total;
     const int y = blockIdx.x >> 4, i = blockIdx.x & 15, lane = threadIdx.x & 31;
@@ -606,7 +695,8 @@ __global__ void __launch_bounds__(256) shared_head_merge_kernel(const float* __r
         const float l = lane < splits ? base[lane * sstride + 1] : 0.0f;
         const float big = warp_max(m);
         const float f = m == -INFINITY ? 0.0f : __expf(m - big);
-        const float total = warp_sum(l * f);
+        float total = warp_sum(l * f);
+        if (sink && total > 0.0f) total += __expf(to_f(sink[g * gs + r % gs]) - big);
         factor[lane] = f;
         if (lane == 0) inv_total = total > 0.0f ? 1.0f / total : 0.0f;
     }
@@ -646,7 +736,7 @@ static size_t shared_head_smem(int dim, int vdim, bool same) {
 template <typename T, int NT>
 static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs,
                               int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* pad, int window, float scale,
-                              void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
+                              float softcap, const void* sink, void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
     const int vdim = 64 * NT;
     const int tiles = (S * (heads / kv_heads) + 15) / 16, splits = shared_head_splits(B, S, heads, kv_heads);
     const bool same = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
@@ -657,23 +747,23 @@ static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k
         auto fn = shared_head_attention_kernel<T, NT, true>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
         fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
-                                        shift, pad, window, scale, ws, splits, tiles, dyn);
+                                        shift, pad, window, scale, softcap, ws, splits, tiles, dyn);
     } else {
         auto fn = shared_head_attention_kernel<T, NT, false>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
         fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
-                                        shift, pad, window, scale, ws, splits, tiles, dyn);
+                                        shift, pad, window, scale, softcap, ws, splits, tiles, dyn);
     }
     if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
-    shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 256, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (T*)out, ld_out, out_col);
+    shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 256, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (const T*)sink, (T*)out, ld_out, out_col);
     return mixers_status();
 }
 
 #define SA_TC_PARAMS const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
-    int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, void* out,     \
-    long ld_out, int out_col, cudaStream_t stream
-#define SA_TC_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, out, \
-    ld_out, out_col, stream
+    int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, float softcap,  \
+    const void* sink, void* out, long ld_out, int out_col, cudaStream_t stream
+#define SA_TC_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, softcap, \
+    sink, out, ld_out, out_col, stream
 
 template <typename T, int KDMAX, int NDMAX>
 static int launch_softmax_tc(SA_TC_PARAMS) {
@@ -685,7 +775,7 @@ static int launch_softmax_tc(SA_TC_PARAMS) {
     }
     softmax_attention_tc_kernel<T, KDMAX, NDMAX><<<grid, 128, smem, stream>>>(
         (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
-        scale, (T*)out, ld_out, out_col);
+        scale, softcap, (const T*)sink, (T*)out, ld_out, out_col);
     return mixers_status();
 }
 
@@ -706,10 +796,30 @@ extern "C" int mixers_latent_prepare(int dtype, const void* proj, int B, int S, 
     return mixers_status();
 }
 
+extern "C" int mixers_wide_qkv_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
+                                       int dim, int vdim, const void* q_w, const void* k_w, float eps, const void* v_other, long ld_other,
+                                       const void* blend, void* q_out, void* k_store, void* v_store, int cap, int held, int shift,
+                                       const int32_t* pad, const int32_t* dyn, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    if (held + S > cap || (v_other && !blend)) return (int)cudaErrorInvalidValue;
+    int threads = 128;
+    if ((long)B * S <= QP_FEW_TOKENS)
+        while (threads < 1024 && threads * QP_MAXC < heads * dim) threads <<= 1;
+#define QP_LAUNCH(TH) MIXERS_DISPATCH(dtype, wide_qkv_prepare_kernel<T, TH><<<(unsigned)(3L * B * S), TH, 0, (cudaStream_t)stream>>>(               \
+        (const T*)proj, B, S, ld, off_q, off_k, off_v, heads, kv_heads, dim, vdim, (const T*)q_w, (const T*)k_w, eps, (const T*)v_other, ld_other, \
+        (const T*)blend, (T*)q_out, (T*)k_store, (T*)v_store, cap, held, shift, pad, dyn))
+    if (threads == 128) QP_LAUNCH(128);
+    else if (threads == 256) QP_LAUNCH(256);
+    else if (threads == 512) QP_LAUNCH(512);
+    else QP_LAUNCH(1024);
+#undef QP_LAUNCH
+    return mixers_status();
+}
+
 extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                                         long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
-                                        int shift, const int32_t* pad, int window, float scale, void* out, long ld_out, int out_col,
-                                        const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream_) {
+                                        int shift, const int32_t* pad, int window, float scale, float softcap, const void* sink, void* out,
+                                        long ld_out, int out_col, const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream_) {
     if (B <= 0 || S <= 0) return 0;
     cudaStream_t stream = (cudaStream_t)stream_;
     const int dim4 = (dim + 3) & ~3;
@@ -722,7 +832,7 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, lon
     const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
     if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && (q_hs & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
         (ld_out & 1) == 0 && (out_col & 1) == 0 && shared_head_smem(dim, vdim, same_kv) <= 227 * 1024) {
-#define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, out, ld_out, out_col, dyn, ws, stream
+#define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, softcap, sink, out, ld_out, out_col, dyn, ws, stream
         if (dtype == 1) return vdim == 128 ? launch_shared_head<__nv_bfloat16, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__nv_bfloat16, 4>(SH_ARGS)
                                                                                                        : launch_shared_head<__nv_bfloat16, 8>(SH_ARGS);
         return vdim == 128 ? launch_shared_head<__half, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__half, 4>(SH_ARGS)
@@ -737,7 +847,7 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, lon
     long items = (long)B * S * heads;
     MIXERS_DISPATCH(dtype, softmax_attention_kernel<T><<<(unsigned)items, SA_WARPS * 32, smem, stream>>>(
         (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
-        scale, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
+        scale, softcap, (const T*)sink, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
     return mixers_status();
 }
 

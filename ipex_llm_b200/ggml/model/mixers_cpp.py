@@ -31,8 +31,17 @@ _SIGNATURES = {
     "mixers_gated_delta_rule": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
                                                                  _c_ptr, _c_ptr],
     "mixers_gated_linear_attention": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
-    "mixers_gated_rms_norm": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_int, _c_int,
+    "mixers_gated_rms_norm": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_int,
                               _c_float, _c_ptr],
+    "mixers_token_shift_mix": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_wkv": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                   _c_ptr],
+    "mixers_layer_norm_residual": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr],
+    "mixers_clamped_glu": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr],
+    "mixers_wide_qkv_prepare": [_c_int, _c_ptr] + [_c_int] * 10 + [_c_ptr, _c_ptr, _c_float, _c_ptr, _c_long, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                                                _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_scored_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                             _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "mixers_poly_norm": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr],
     "mixers_soft_cap": [_c_int, _c_ptr, _c_long, _c_float, _c_ptr, _c_ptr],
     "mixers_embed_pair": [_c_int, _c_ptr, _c_float, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr,
@@ -46,12 +55,12 @@ _SIGNATURES = {
     "mixers_latent_prepare": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
-                                + [_c_ptr, _c_int, _c_float, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
+                                + [_c_ptr, _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
-                         _c_ptr, _c_ptr, _c_ptr],
+                         _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_sort": [_c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
-    "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 
 

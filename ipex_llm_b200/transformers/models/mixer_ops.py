@@ -110,13 +110,72 @@ def gated_linear_attention(proj, heads, dim, vdim, z, tau, state, slot0, pad):
 
 
 def gated_rms_norm(o, gate, off_g, weight, eps, out, out_col, out_scale):
-    """out[:, out_col:...] = out_scale * rms_norm(o per head) * weight * silu(gate columns from off_g)"""
+    """out[:, out_col:...] = out_scale * rms_norm(o per head) * weight * silu(gate columns from off_g); ``weight`` [vdim] serves
+    every head, [heads * vdim] gives each head its own"""
     heads, vdim = o.shape[-2], o.shape[-1]
     n = o.numel() // (heads * vdim)
     invalidInputError(o.is_contiguous() and o.dtype == torch.float32 and gate.is_contiguous() and out.is_contiguous() and out.shape[0] == n
-                      and gate.dtype == out.dtype, "gated_rms_norm: unexpected layout")
+                      and gate.dtype == out.dtype and weight.numel() in (vdim, heads * vdim), "gated_rms_norm: unexpected layout")
     native.call("mixers_gated_rms_norm", native.dtype_code(out.dtype), native.ptr(o), n, heads, vdim, native.ptr(gate), gate.shape[-1], off_g,
-                native.ptr(weight), float(eps), native.ptr(out), out.shape[1], out_col, float(out_scale), native.stream(out.device))
+                native.ptr(weight), vdim if weight.numel() == heads * vdim and heads > 1 else 0, float(eps), native.ptr(out), out.shape[1], out_col,
+                float(out_scale), native.stream(out.device))
+
+
+def token_shift_mix(h, mu, tail, tail_next, slot0, pad):
+    """[n_mix, B * S, C]: h + (previous h - h) * mu[m] for every mixing vector; ``tail`` [B, 1, C] holds the token before the
+    call's first one, ``tail_next`` receives the call's last one"""
+    B, S, C = h.shape
+    invalidInputError(h.is_contiguous() and mu.is_contiguous() and mu.shape[1] == C and mu.dtype == h.dtype and tail.shape == (B, 1, C)
+                      and tail.dtype == h.dtype and tail.is_contiguous() and tail_next.is_contiguous(), "token_shift_mix: unexpected layout")
+    out = torch.empty(mu.shape[0], B * S, C, dtype=h.dtype, device=h.device)
+    native.call("mixers_token_shift_mix", native.dtype_code(h.dtype), native.ptr(h), B, S, C, native.ptr(mu), mu.shape[0], native.ptr(tail),
+                native.ptr(tail_next), int(slot0), native.ptr(pad), native.ptr(out), native.stream(h.device))
+    return out
+
+
+def wkv(r, k, v, B, S, heads, dim, z, w0, u, state, slot0, pad):
+    """the RWKV-style recurrence over the new tokens; r, k, v [B * S, heads * dim] views with one row stride (parts of one
+    buffer), z [B * S, heads * dim] decay logits; state fp32 [B, heads, dim, dim] in place; returns o fp32 [B, S, heads, dim]"""
+    ld = r.stride(0)
+    invalidInputError(k.stride(0) == ld and v.stride(0) == ld and r.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+                      and r.dtype == k.dtype == v.dtype == z.dtype and z.is_contiguous() and z.shape == (B * S, heads * dim)
+                      and w0.numel() == heads * dim and u.numel() == heads * dim and w0.is_contiguous() and u.is_contiguous()
+                      and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (B, heads, dim, dim),
+                      "wkv: unexpected layout")
+    o = torch.empty(B, S, heads, dim, dtype=torch.float32, device=r.device)
+    native.call("mixers_wkv", native.dtype_code(r.dtype), native.ptr(r), native.ptr(k), native.ptr(v), B, S, ld, heads, dim, native.ptr(z),
+                native.ptr(w0), native.ptr(u), native.ptr(state), int(slot0), native.ptr(pad), native.ptr(o), native.stream(r.device))
+    return o
+
+
+def layer_norm_residual(x, y_a, y_b, weight, eps, out_dtype, want_out=True):
+    """x += y_a + y_b in place (x fp32 [N, W]; y_a in the model's dtype, y_b fp32, either may be None); returns the layer norm
+    (weight only) of the new x in ``out_dtype``, or None without ``want_out``"""
+    n, w = x.shape
+    invalidInputError(x.dtype == torch.float32 and x.is_contiguous() and (y_a is None or (y_a.shape == x.shape and y_a.dtype == out_dtype and y_a.is_contiguous()))
+                      and (y_b is None or (y_b.shape == x.shape and y_b.dtype == torch.float32 and y_b.is_contiguous())),
+                      "layer_norm_residual: x a contiguous fp32 [N, W], y_a the model's dtype, y_b fp32")
+    out = torch.empty(n, w, dtype=out_dtype, device=x.device) if want_out else None
+    native.call("mixers_layer_norm_residual", native.dtype_code(out_dtype), native.ptr(x), n, w, native.ptr(y_a), native.ptr(y_b),
+                native.ptr(weight) if want_out else None, float(eps), native.ptr(out), native.stream(x.device))
+    return out
+
+
+def wide_qkv_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w, k_w, eps, v_other, blend, k_store, v_store, cap, held, shift,
+                     pad, dyn=None):
+    """RMS norm over the whole query and the whole key projection of every new token, values blended with ``v_other`` (a
+    [B * S, kv_heads * vdim] view with unit column stride, or None), cache write of keys and values; returns q [B * S, heads * dim]"""
+    B, S, P = proj.shape
+    invalidInputError(proj.is_contiguous() and k_store.is_contiguous() and v_store.is_contiguous() and k_store.shape[2] == cap
+                      and v_store.shape[2] == cap and k_store.dtype == proj.dtype and v_store.dtype == proj.dtype
+                      and (v_other is None or (v_other.stride(1) == 1 and v_other.shape == (B * S, kv_heads * vdim) and v_other.dtype == proj.dtype)),
+                      "wide_qkv_prepare: unexpected layout")
+    q = torch.empty(B * S, heads * dim, dtype=proj.dtype, device=proj.device)
+    native.call("mixers_wide_qkv_prepare", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off_q, off_k, off_v, heads, kv_heads, dim, vdim,
+                native.ptr(q_w), native.ptr(k_w), float(eps), native.ptr(v_other), v_other.stride(0) if v_other is not None else 0,
+                native.ptr(blend) if v_other is not None else None, native.ptr(q), native.ptr(k_store), native.ptr(v_store), cap, int(held), int(shift),
+                native.ptr(pad), native.ptr(dyn), native.stream(proj.device))
+    return q
 
 
 def poly_norm(z, coef, eps):
@@ -216,21 +275,25 @@ def latent_prepare(proj, off_q, q_rank, q_w, off_c, kv_rank, c_w, eps, store, he
     return cq
 
 
-def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out=None, out_col=0, dyn=None, tensor_cores=True):
+def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out=None, out_col=0, dyn=None, tensor_cores=True, softcap=0.0,
+                      sink=None):
     """q [B * S, heads * dim], or [B * S, heads, dim] with any token and head strides; k [B, L, kv_heads, dim], v [B, L, kv_heads,
-    vdim] views (any strides with a unit last one); returns out [B * S, heads * vdim] in q's dtype"""
+    vdim] views (any strides with a unit last one); returns out [B * S, heads * vdim] in q's dtype.  ``softcap`` > 0 caps the
+    scaled scores (cap * tanh(score / cap)); ``sink`` [heads]: a per-head term exp(sink) in the softmax's denominator"""
     kv_heads, dim, vdim = k.shape[2], k.shape[3], v.shape[3]
     q_hs = q.stride(1) if q.dim() == 3 else dim
     invalidInputError(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.numel() == B * S * heads * dim and k.dtype == q.dtype
                       and v.dtype == q.dtype and v.shape[2] == kv_heads and (dyn is not None or (k.shape[1] >= held + S and v.shape[1] >= held + S)),
                       "softmax_attention: unexpected layout")
+    invalidInputError(sink is None or (sink.numel() == heads and sink.dtype == q.dtype and sink.is_contiguous()), "softmax_attention: one sink per head")
     if out is None:
         out = torch.empty(B * S, heads * vdim, dtype=q.dtype, device=q.device)
     need = native.lib().mixers_softmax_attention_workspace(native.dtype_code(q.dtype), B, S, heads, kv_heads, dim, vdim) if tensor_cores else 0
     ws = torch.empty(need, dtype=torch.float32, device=q.device) if need else None
     native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), q_hs, native.ptr(k), k.stride(0), k.stride(1),
                 k.stride(2), native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift),
-                native.ptr(pad), int(window), float(scale), native.ptr(out), out.stride(0), int(out_col), native.ptr(dyn), int(bool(tensor_cores)),
+                native.ptr(pad), int(window), float(scale), float(softcap or 0.0), native.ptr(sink), native.ptr(out), out.stride(0), int(out_col),
+                native.ptr(dyn), int(bool(tensor_cores)),
                 native.ptr(ws), native.stream(q.device))
     return out
 
@@ -248,17 +311,50 @@ def grouped_router(h, router, correction, groups, keep, top):
     return idx, wgt
 
 
-def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out, ffs=None, always_on=False):
+def scored_router(h, router, correction, groups, keep, top, sigmoid=True, group_top=2, renorm=True, scale=1.0, gate_row=None):
+    """(chosen outputs int32 [N, top], weights fp32 [N, top], gate fp32 [N] or None).  Scores: a sigmoid per output (or the
+    softmax over all); groups ranked by the sum of their ``group_top`` best choice scores; weights = the winners' scores, over
+    their sum if ``renorm``, times ``scale``; ``gate_row`` [1, W]: gate = sigmoid(gate_row . h) for an expert every token runs"""
+    h = _c(h)
+    n, w = h.shape
+    invalidInputError(router.is_contiguous() and router.shape[1] == w and router.dtype == h.dtype and correction.dtype == h.dtype
+                      and correction.numel() == router.shape[0] and (gate_row is None or (gate_row.numel() == w and gate_row.dtype == h.dtype
+                                                                                           and gate_row.is_contiguous())),
+                      "scored_router: unexpected layout")
+    idx = torch.empty(n, top, dtype=torch.int32, device=h.device)
+    wgt = torch.empty(n, top, dtype=torch.float32, device=h.device)
+    gate = torch.empty(n, dtype=torch.float32, device=h.device) if gate_row is not None else None
+    native.call("mixers_scored_router", native.dtype_code(h.dtype), native.ptr(h), n, w, native.ptr(router), native.ptr(correction), router.shape[0],
+                int(groups), int(keep), int(top), int(bool(sigmoid)), int(group_top), int(bool(renorm)), float(scale), native.ptr(gate_row),
+                native.ptr(gate), native.ptr(idx), native.ptr(wgt), native.stream(h.device))
+    return idx, wgt, gate
+
+
+def clamped_glu(gate_up, cols, limit):
+    """g' sigmoid(1.702 g') (u' + 1): g' = the first ``cols`` columns capped at ``limit``, u' = the next ``cols`` clamped to +-limit"""
+    gate_up = _c(gate_up)
+    n = gate_up.numel() // gate_up.shape[-1]
+    out = torch.empty(n, cols, dtype=gate_up.dtype, device=gate_up.device)
+    if n:
+        native.call("mixers_clamped_glu", native.dtype_code(gate_up.dtype), native.ptr(gate_up), n, gate_up.shape[-1], 0, cols, cols, float(limit),
+                    native.ptr(out), native.stream(out.device))
+    return out
+
+
+def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out, ffs=None, always_on=False, always_w=None, clamped=False,
+              limit=0.0, limit_always=0.0):
     """fp32 [N, W]: the chosen experts of a few tokens through tables of the experts' weight addresses.  ``ffs``: int32 sizes per
-    table entry (``ff`` = the largest); ``always_on``: table entry ``n_experts`` is an expert every token runs with weight 1"""
+    table entry (``ff`` = the largest); ``always_on``: table entry ``n_experts`` is an expert every token runs, with weight
+    ``always_w`` [N] (None: 1); ``clamped``: the experts' activation is the clamped form with ``limit`` (``limit_always`` for the
+    always-on expert) instead of silu(g) u"""
     h = _c(h)
     n, w = h.shape
     top = idx.shape[1]
     act = torch.empty(max(n * (top + int(always_on)) * ff, 1), dtype=h.dtype, device=h.device)
     y = torch.empty(n, w, dtype=torch.float32, device=h.device)
     native.call("mixers_moe_small", native.dtype_code(h.dtype), native.ptr(h), n, w, int(ff), top, int(n_experts), int(n_out), native.ptr(idx),
-                native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(ffs), int(bool(always_on)), native.ptr(shared_out),
-                native.ptr(act), native.ptr(y), native.stream(h.device))
+                native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(ffs), int(bool(always_on)), native.ptr(always_w),
+                int(bool(clamped)), float(limit), float(limit_always), native.ptr(shared_out), native.ptr(act), native.ptr(y), native.stream(h.device))
     return y
 
 
@@ -274,11 +370,12 @@ def moe_sort(idx, n_keys):
     return counts, pos, token_of
 
 
-def moe_combine(rows, pos, idx, wgt, h, shared_out, n_experts, n_out):
-    """fp32 [N, W]: weighted sum of the experts' outputs ``rows`` (row pos[n, k] belongs to token n's k-th choice)"""
+def moe_combine(rows, pos, idx, wgt, h, shared_out, n_experts, n_out, shared_w=None):
+    """fp32 [N, W]: weighted sum of the experts' outputs ``rows`` (row pos[n, k] belongs to token n's k-th choice) + shared_out
+    (times ``shared_w`` [N] when given)"""
     h = _c(h)
     n, w = h.shape
     y = torch.empty(n, w, dtype=torch.float32, device=h.device)
     native.call("mixers_moe_combine", native.dtype_code(h.dtype), native.ptr(rows), native.ptr(pos), native.ptr(idx), native.ptr(wgt), native.ptr(h),
-                native.ptr(shared_out), n, w, idx.shape[1], int(n_experts), int(n_out), native.ptr(y), native.stream(h.device))
+                native.ptr(shared_out), native.ptr(shared_w), n, w, idx.shape[1], int(n_experts), int(n_out), native.ptr(y), native.stream(h.device))
     return y
