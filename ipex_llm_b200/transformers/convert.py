@@ -169,6 +169,12 @@ def _optimize_pre(model, qtype=None):
         # the query-latent and key/value-latent projections read the same input -> one in_proj
         from ipex_llm_b200.transformers.models.serotar import merge_projections
         model.apply(merge_projections)
+    elif model_type == "zubedra":
+        # the query, key and value projections of an attention mixer read the same input -> one in_proj
+        # (and, when no low-bit conversion follows, a wkv mixer's four wide projections -> one batched product)
+        import functools
+        from ipex_llm_b200.transformers.models.zubedra import merge_projections
+        model.apply(functools.partial(merge_projections, stack=qtype is None))
     return model
 
 
@@ -200,7 +206,7 @@ def _optimize_post(model):
         convert_forward(model, module.MixtralRMSNorm, rms_norm_forward)
         convert_forward(model, module.MixtralModel, mixtral_model_forward)
         convert_forward(model, module.MixtralAttention, mixtral_attention_forward)
-    elif model_type in ("zafepel", "serotar"):
+    elif model_type in ("zafepel", "serotar", "zubedra"):
         # this package's own model class: its forwards already call the fused operators and pick the state cache;
         # the recorded decode step for such a cache goes behind generate()
         from ipex_llm_b200.transformers.state_decode_graph import install_state_generate

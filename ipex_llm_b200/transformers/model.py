@@ -37,7 +37,8 @@ def save_low_bit(self, save_dir, *args, **kwargs):
 # designs that no library ships: config.json's "architecture" -> the module of this package that defines the model
 # (``load_pretrained(model_dir, torch_dtype)`` builds it from config.json + model.safetensors)
 NATIVE_ARCHITECTURES = {"Zafepel": "ipex_llm_b200.transformers.models.zafepel",
-                        "Serotar": "ipex_llm_b200.transformers.models.serotar"}
+                        "Serotar": "ipex_llm_b200.transformers.models.serotar",
+                        "Zubedra": "ipex_llm_b200.transformers.models.zubedra"}
 
 
 def native_architecture(model_dir):
