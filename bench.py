@@ -687,11 +687,11 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-tp", action="store_true")
     ap.add_argument("--fused-mlp", type=int, default=1, dest="fused_mlp")
-    ap.add_argument("--arch", default="llama", choices=["llama", "zafepel", "serotar"],
-                    help="llama: the headline workload (default, unchanged); zafepel / serotar: that design at real layer sizes beside "
-                         "the closest model of equal size (a Llama / a Mixtral), with every kernel of the design against its roofline "
-                         "(bench_mixers.py / bench_serotar.py)")
-    ap.add_argument("--no-compare", action="store_true", help="--arch zafepel / serotar: leave out the model of equal size")
+    ap.add_argument("--arch", default="llama", choices=["llama", "zafepel", "serotar", "zubedra"],
+                    help="llama: the headline workload (default, unchanged); zafepel / serotar / zubedra: that design at real layer sizes "
+                         "beside the closest model of equal size (a Llama / a Mixtral / a Serotar), with every kernel of the design against "
+                         "its roofline (bench_mixers.py / bench_serotar.py / bench_zubedra.py)")
+    ap.add_argument("--no-compare", action="store_true", help="--arch zafepel / serotar / zubedra: leave out the model of equal size")
     args = ap.parse_args()
     if args.arch == "zafepel":
         import bench_mixers
@@ -700,6 +700,10 @@ def main():
     if args.arch == "serotar":
         import bench_serotar
         bench_serotar.run(args)
+        return
+    if args.arch == "zubedra":
+        import bench_zubedra
+        bench_zubedra.run(args)
         return
     global FUSED_MLP
     FUSED_MLP = bool(args.fused_mlp)
