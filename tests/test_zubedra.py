@@ -617,6 +617,38 @@ def test_greedy_generate_matches_the_oracle(tmp_path, cuda_device, name):
 
 
 @pytest.mark.gpu
+def test_recorded_step_of_a_16_bit_model_equals_the_eager_loop(tmp_path, cuda_device, monkeypatch):
+    """a bf16 model whose decoding attention is the kernel that splits the keys of shared heads over blocks (8 heads on 2, values
+    of 128): the replayed step reads the cache length from the device and must produce the tokens of the loop that passes it
+    from the host; the recurrence's state and tail are updated in place by both"""
+    cfg = O.random_config(width=64, vocab=70, kinds=("attention", "wkv", "attention"), heads=8, kv_heads=2, dim=16, vdim=128, scale=0.25, softcap=10.0,
+                          wkv_heads=2, wkv_dim=32, experts=4, groups=(2, 1), top=2, expert_ff=16, shared_ff=16)
+    w = O.random_weights(cfg, 5)
+    save_checkpoint(cfg, w, tmp_path / "m")
+    model = load_framework(tmp_path / "m", torch.bfloat16, cuda_device)
+    from ipex_llm_b200.ggml.model import mixers_cpp
+    assert mixers_cpp.lib().mixers_softmax_attention_workspace(mixers_cpp.dtype_code(torch.bfloat16), 2, 1, 8, 2, 16, 128) > 0
+    prompts = torch.tensor([tokens_for(cfg, 70, 1), [0] * 30 + tokens_for(cfg, 40, 2)], device=cuda_device)
+    mask = torch.tensor([[1] * 70, [0] * 30 + [1] * 40], device=cuda_device)
+    replayed = model.generate(prompts, attention_mask=mask, max_new_tokens=80, do_sample=False)
+    assert model.__dict__.get("_b200_state_graph_failed") is None and model.__dict__.get("_b200_state_graphs")
+    monkeypatch.setenv("IPEX_LLM_B200_DECODE_GRAPH", "0")
+    eager = model.generate(prompts, attention_mask=mask, max_new_tokens=80, do_sample=False)
+    assert torch.equal(replayed, eager)
+    # and both follow the plain statement as far as a 16-bit model can: the first new token of each row
+    for b, n in ((0, 70), (1, 40)):
+        want = O.forward(cfg, w64(w), prompts[b, 70 - n:].tolist())[-1]
+        top2 = want.topk(2).values
+        if top2[0] - top2[1] > 0.5:
+            assert int(replayed[b, 70]) == int(want.argmax())
+    # the same model against the oracle position by position, decoding through the split-key kernel
+    tokens = tokens_for(cfg, 60, 7)
+    margins = []
+    want = O.forward(cfg, w64(w), tokens, None, margins)
+    assert_close(run_portions(model, tokens, [30, 1], cuda_device), want, torch.bfloat16, clear_choices(margins))
+
+
+@pytest.mark.gpu
 def test_low_bit_conversion_runs_the_same_model(tmp_path, cuda_device, native_lib):
     """the projections are ordinary linears to the converter: a sym_int4 model answers close to the 16-bit one; its experts (no
     longer plain matrices) take the sorted path also for one token, the narrow decay projection stays a plain matrix"""
