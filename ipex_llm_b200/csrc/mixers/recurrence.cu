@@ -218,8 +218,12 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
     }
 }
 
-template <typename T, int MODE, int R>                     // MODE 0: gated delta rule, 1: gated linear attention
-__global__ void __launch_bounds__(REC_THREADS) linear_recurrence_kernel(RecArgs a) {
+// MINB: blocks that must fit an SM together.  0 (no demand) leaves the choice of registers to the compiler (a grid of at most
+// one block per SM: what counts is how fast ONE block walks its tokens; demanding 1 explicitly made it take more registers and
+// run 10 % slower); 2 halves them (some spills) so that two blocks hide each other's latencies, which pays when the grid has
+// more blocks than the GPU has SMs (batches, many heads): measured for the wkv mode only.
+template <typename T, int MODE, int R, int MINB>           // MODE 0: gated delta rule, 1: gated linear attention, 2: wkv
+__global__ void __launch_bounds__(REC_THREADS, MINB) linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sh[];
     const int lpc = a.lpc, dp = R * lpc, tc = a.tc;
     const int cols_blk = REC_CONSUMERS / lpc;
@@ -492,9 +496,11 @@ static int launch_recurrence(RecArgs a, cudaStream_t stream) {
     if (bytes > 160 * 1024) return launch_recurrence_few<T, MODE>(a, stream);  // very wide heads: stages of fewer tokens, unpipelined
     a.lpc = lpc; a.tc = REC_TC;
     dim3 grid((a.vdim + cols_blk - 1) / cols_blk, a.heads, a.B);
-    auto kernel = r == 16 ? linear_recurrence_kernel<T, MODE, 16> : linear_recurrence_kernel<T, MODE, 32>;
-    static size_t allowed[2] = {48 * 1024, 48 * 1024};       // per instantiation (r == 16, r == 32): raised once, outside any capture
-    size_t& cur = allowed[r == 16 ? 0 : 1];
+    const bool pair = MODE == 2 && (long)grid.x * grid.y * grid.z > 148 && 2 * bytes <= 200 * 1024;
+    auto kernel = r == 16 ? (pair ? linear_recurrence_kernel<T, MODE, 16, 2> : linear_recurrence_kernel<T, MODE, 16, 0>)
+                          : (pair ? linear_recurrence_kernel<T, MODE, 32, 2> : linear_recurrence_kernel<T, MODE, 32, 0>);
+    static size_t allowed[4] = {48 * 1024, 48 * 1024, 48 * 1024, 48 * 1024};   // per instantiation: raised once, outside any capture
+    size_t& cur = allowed[(r == 16 ? 0 : 1) + (pair ? 2 : 0)];
     if (bytes > cur) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
