@@ -385,6 +385,9 @@ def load_pretrained(model_dir, torch_dtype=None, device=None):
     for dst, src in checkpoint_key_map(config).items():
         names = [src] if isinstance(src, str) else list(src)
         missing = [s for s in names if s not in tensors]
+        if missing and dst.endswith(".vmix"):                                # a layer that blends nothing may come without its weight
+            state[dst] = torch.zeros((), dtype=torch_dtype)
+            continue
         invalidInputError(not missing, f"the checkpoint has no tensor {missing}")
         if isinstance(src, str):
             t = tensors[src]
@@ -395,6 +398,8 @@ def load_pretrained(model_dir, torch_dtype=None, device=None):
         state[dst] = t.to(torch_dtype)
     for name, p in model.named_parameters():
         invalidInputError(name in state, f"no checkpoint tensor for parameter {name}")
+        if tuple(state[name].shape) != tuple(p.shape) and [d for d in state[name].shape if d != 1] == [d for d in p.shape if d != 1]:
+            state[name] = state[name].reshape(p.shape)                       # the same numbers with or without axes of length 1
         invalidInputError(tuple(state[name].shape) == tuple(p.shape),
                           f"{name}: checkpoint shape {tuple(state[name].shape)} but the configuration gives {tuple(p.shape)}")
     model.load_state_dict(state, strict=True, assign=True)

@@ -138,6 +138,10 @@ def test_loader_maps_every_tensor_and_merges(tmp_path):
     plain = load_framework(tmp_path / "plain", torch.float32)
     assert plain.model.layers[1].mlp is None and plain.model.layers[0].mlp.shared is None and plain.model.layers[0].mlp.groups == 1
     assert plain.config.first_blending_layer() is None and plain.config.wkv_ranks == {"0": 3, "2": 3}
+    # a layer that blends nothing may come without a blending weight
+    del w2["l1.mix.vmix"]
+    save_checkpoint(cfg2, w2, tmp_path / "noblend")
+    assert load_framework(tmp_path / "noblend", torch.float32).model.layers[1].mixer.vmix.item() == 0.0
     # a tensor of the wrong shape is refused, by name
     bad = dict(w)
     bad["l1.mlp.correction"] = torch.zeros(4, dtype=torch.bfloat16)
