@@ -51,6 +51,10 @@ int mixers_sigmoid_window_attention(int dtype, const float* q, const void* k_sto
  * be null: none of the new tokens is padding (true for every call but a batch's first). */
 int mixers_short_conv_silu(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w,
                            const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream);
+/* the same taps with a bias per channel (may be null) and flags: bit 0 = silu on the result, bit 1 = the token's own input is
+ * added to the result, y = in(t) + conv (a convolution that refines what a mixer reads instead of replacing it) */
+int mixers_short_conv(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w, const void* bias,
+                      int flags, const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream);
 
 /* Gated delta rule.  conv [B, S, C]: q | k (kv_heads x dim each) | v (heads x vdim) after the short convolution; q and k are
  * made unit vectors here (q also times dim^-1/2).  beta = sigmoid(proj[.., off_b + h]), decay = exp(-exp(A_log[h]) *
@@ -60,16 +64,51 @@ int mixers_gated_delta_rule(int dtype, const void* conv, int B, int S, int kv_he
                             const void* proj, int ld, int off_b, int off_a, const void* A_log, const void* dt_bias, float* state,
                             int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
 
+/* Delta rule whose state decays per key channel.  conv as above; beta = sigmoid(proj[.., off_b + h]); z [B, S, heads * dim]: decay
+ * logits, a = exp(-exp(A_log[h]) * softplus(z + dt_bias)) with dt_bias [heads * dim].  Per head:  M <- diag(a) M;
+ * u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q (q, k unit vectors, q times dim^-1/2). */
+int mixers_channel_delta_rule(int dtype, const void* conv, int B, int S, int kv_heads, int heads, int dim, int vdim, const void* proj,
+                              int ld, int off_b, const void* z, const void* A_log, const void* dt_bias, float* state, int slot0,
+                              const int32_t* pad, float* o, mixers_stream_t stream);
+
+/* State-space scan with a scalar decay per head.  conv [B, S, C]: x (heads x vdim) | B (groups x n_state) | C (groups x n_state)
+ * after the short convolution; dt = softplus(proj[.., off_dt + h] + dt_bias[h]).  Per head (its group's B and C):
+ * M <- exp(-exp(A_log[h]) dt) M + dt B x^T;  o = M^T C + skip[h] x.  state: float [B, heads, n_state, vdim]. */
+int mixers_state_space_scan(int dtype, const void* conv, int B, int S, int groups, int heads, int n_state, int vdim, const void* proj,
+                            int ld, int off_dt, const void* A_log, const void* dt_bias, const void* skip, float* state, int slot0,
+                            const int32_t* pad, float* o, mixers_stream_t stream);
+
 /* Gated linear attention.  proj [B, S, ld]: q | k (heads x dim each) | v (heads x vdim) from column 0; z [B, S, heads * dim]:
  * decay logits, alpha = sigmoid(z)^(1/tau).  Per head:  M <- diag(alpha) M + k v^T;  o = M^T (q dim^-1/2). */
 int mixers_gated_linear_attention(int dtype, const void* proj, int B, int S, int ld, int heads, int dim, int vdim, const void* z,
                                   float tau, float* state, int slot0, const int32_t* pad, float* o, mixers_stream_t stream);
 
 /* out[n, out_col + h * vdim + c] = out_scale * o[n, h, c] / rms(o[n, h, :]) * w[h * w_head_stride + c] * silu(gate[n, off_g + h * vdim + c])
- * (w_head_stride 0: one weight vector [vdim] for every head; vdim: a vector per head, [heads * vdim]) */
+ * (w_head_stride 0: one weight vector [vdim] for every head; vdim: a vector per head, [heads * vdim]).  gate_mode bit 0: the gate
+ * is sigmoid(.) instead of silu(.); bit 1: the gate multiplies before the norm, i.e. rms is taken of o * gate. */
 int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
                           const void* w, int w_head_stride, float eps, void* out, int ld_out, int out_col, float out_scale,
-                          mixers_stream_t stream);
+                          int gate_mode, mixers_stream_t stream);
+
+/* o[n, c] *= sigmoid(gate[n, off_g + c / per_gate]) in place, o dtype [n_rows, cols] */
+int mixers_sigmoid_gate(int dtype, void* o, long n_rows, int cols, const void* gate, int ld_gate, int off_g, int per_gate,
+                        mixers_stream_t stream);
+
+/* out float [n_rows, width] = scale * (a / rms(a) * w_a + b / rms(b) * w_b): two branch outputs meet as normalised vectors */
+int mixers_rms_pair_sum(int dtype, const void* a, const void* b, const void* w_a, const void* w_b, float eps, float scale, long n_rows,
+                        int width, float* out, mixers_stream_t stream);
+
+/* The boundary between layers whose mixer and feed-forward read two scalar-gain RMS norms of the same stream x (float
+ * [n_rows, width], in place):  x += y_a + y_c + y_b + y_d (dtype, dtype, float, float; each may be null);  with pre_gain:
+ * x <- x / rms(x) * pre_gain[0] (the norm behind an embedding);  with stack (float [streams, n_rows, width]): the new x is kept
+ * as stream `index` and, with coef (dtype [index + 1]), replaced by sum_j coef[j] * stack[j];  h1 = x / rms(x) * gain1[0],
+ * h2 = x / rms(x) * gain2[0] in dtype (either may be null). */
+int mixers_sum_residual_norms(int dtype, float* x, long n_rows, int width, const void* y_a, const void* y_c, const float* y_b,
+                              const float* y_d, const void* pre_gain, float eps, float* stack, long stack_stride, int index,
+                              const void* coef, const void* gain1, const void* gain2, void* h1, void* h2, mixers_stream_t stream);
+
+/* out = exact (erf) gelu of in, n elements */
+int mixers_gelu_erf(int dtype, const void* in, long n, void* out, mixers_stream_t stream);
 
 /* Token shift.  out[m, n, c] = h[n, c] + (h[n - 1, c] - h[n, c]) * mu[m, c], m < n_mix: h dtype [B, S, C], mu [n_mix, C], out
  * [n_mix, B * S, C].  The token before a call's first one is tail [B, 1, C] (zeros before a sequence's first token); padding
@@ -148,9 +187,23 @@ int mixers_wide_qkv_prepare(int dtype, const void* proj, int B, int S, int ld, i
                             const void* blend, void* q_out, void* k_store, void* v_store, int cap, int held, int shift,
                             const int32_t* pad, const int32_t* dyn, mixers_stream_t stream);
 
+/* Rotary positions and cache write for the new tokens' queries and keys (columns of proj [B, S, ld]): `heads` query heads of q_dim
+ * channels from off_q, `kv_heads` key heads of k_dim channels from off_k and, if vdim > 0, `kv_heads` value heads from off_v.
+ * Inside a head channel rot_off + i pairs with rot_off + i + rot_dims / 2: (u, v) -> (u cos a - v sin a, v cos a + u sin a) * amp,
+ * a = position * inv_freq[i] (doubles; angle, sine and cosine in double precision).  k_norm_w (may be null): the first
+ * k_norm_cols channels of a key head are divided by their root mean square (eps) and multiplied by k_norm_w first.  q_out dtype
+ * [B * S, heads * q_dim]; key of row b, storage index j, head g at k_store + b * k_bs + j * k_ps + g * k_hs (values alike);
+ * the new tokens go to index held + t; padding slots store zeros.  dyn as in mixers_window_qk_prepare. */
+int mixers_rope_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
+                           int q_dim, int k_dim, int vdim, int q_rot_off, int k_rot_off, int rot_dims, const double* inv_freq, float amp,
+                           const void* k_norm_w, int k_norm_cols, float eps, void* q_out, void* k_store, long k_bs, long k_ps, long k_hs,
+                           void* v_store, long v_bs, long v_ps, long v_hs, int held, int shift, const int32_t* pad, const int32_t* dyn,
+                           mixers_stream_t stream);
+
 /* Causal softmax attention of S new tokens per row.  q: head h of token n at q + n * q_ld + h * q_hs.  Key (value) of storage
  * index j, row b, kv head g at k + b * k_bs + j * k_ps + g * k_hs (strides in elements).  The query at storage index c = held
- * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window.  Scores
+ * + t sees the keys j <= c of its row that are not padding (j + shift >= pad[b]) and, if window > 0, c - j < window, and, if
+ * chunk > 0, only keys whose position p_j has floor(p_j / chunk) = floor(p_c / chunk) (positions count from the row's first token).  Scores
  * (q . k) * scale -- then softcap * tanh(score / softcap) if softcap > 0 -- and the softmax weights are 32-bit.  sink (dtype
  * [heads], may be null): the denominator of head h's softmax also holds exp(sink[h]), which has no key and no value.  out[n, out_col + h * vdim + :] in dtype (zeros for padding queries).
  * allow_tensor_cores: 16-bit models may take the tensor-core kernels: for S >= 16 one block per 64 tokens of a head (head sizes
@@ -159,7 +212,7 @@ int mixers_wide_qkv_prepare(int dtype, const void* proj, int B, int S, int ld, i
  * mixers_softmax_attention_workspace(...) floats (0: these sizes never take that kernel).  dyn as above. */
 int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                              long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
-                             int shift, const int32_t* pad, int window, float scale, float softcap, const void* sink, void* out,
+                             int shift, const int32_t* pad, int window, int chunk, float scale, float softcap, const void* sink, void* out,
                              long ld_out, int out_col, const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream);
 long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int kv_heads, int dim, int vdim);
 
@@ -167,7 +220,7 @@ long mixers_softmax_attention_workspace(int dtype, int B, int S, int heads, int 
  * all n_out outputs (score_mode 0) or sigmoid(z) each (score_mode 1); choice = s + correction.  Outputs [g * n_out / groups,
  * (g + 1) * n_out / groups) are group g; groups are ranked by the sum of their group_top largest choice scores, the `keep` first
  * groups stay eligible (every other output is out of the running, whatever its sign), and the `top` eligible outputs of highest
- * choice win (the lower index on a tie).  idx_out int32 [n_rows, top] (n_out where nothing was left to choose); w_out float
+ * choice win (the lower index on a tie); correction may be null (none).  idx_out int32 [n_rows, top] (n_out where nothing was left to choose); w_out float
  * [n_rows, top] = s of the chosen, divided by their sum + 1e-20 if renorm, times w_scale.  gate_row (dtype [width], may be null):
  * gate_out[n] = sigmoid(gate_row . h[n]), the gate of an expert that every token runs. */
 int mixers_scored_router(int dtype, const void* h, long n_rows, int width, const void* router, const void* correction, int n_out,
@@ -181,13 +234,15 @@ int mixers_grouped_router(int dtype, const void* h, long n_rows, int width, cons
  * then up rows) and [width, ff_e] matrices in dtype; ffs[e] = ff_e (null: `ff` for all; `ff` is the largest).  always_on != 0:
  * table entry n_experts is an expert that every token runs (a shared expert) with weight always_w[n] (null: 1).  act: scratch dtype
  * [n_rows, top + (always_on ? 1 : 0), ff].  The experts' activation A(g, u): act_kind 0 = silu(g) u; 1 = g' sigmoid(1.702 g')
- * (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), L = `limit` for chosen experts and `limit_always` for the always-on one.
+ * (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), L = `limit` for chosen experts and `limit_always` for the always-on one;
+ * 2 = no gate, the exact gelu of u, the first matrix being [ff_e, width].  weight_input != 0: a chosen expert's weight multiplies
+ * its INPUT (w_k h rounded to dtype) instead of its output.
  * y float [n_rows, width] = sum_k w_k * down_e A(gate_e h, up_e h) for chosen e < n_experts, w_k * h for n_experts <= e < n_out,
  * + the always-on expert, + shared_out (dtype [n_rows, width], may be null). */
 int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
                      const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
-                     const float* always_w, int act_kind, float limit, float limit_always, const void* shared_out, void* act, float* y,
-                     mixers_stream_t stream);
+                     const float* always_w, int act_kind, int weight_input, float limit, float limit_always, const void* shared_out,
+                     void* act, float* y, mixers_stream_t stream);
 
 /* Counting sort of n_pairs = n_rows * top (token, choice) pairs by chosen output idx[i] in [0, n_keys): counts[e] = pairs of e;
  * pos[i] = row of pair i among the sorted pairs; token_of[row] = i / top. */
@@ -195,10 +250,16 @@ int mixers_moe_sort(const int32_t* idx, long n_pairs, int top, int n_keys, int32
                     mixers_stream_t stream);
 
 /* y float [n_rows, width] = sum_k w[n, k] * rows[pos[n, k], :] for chosen e < n_experts, w * h[n, :] for identity experts,
- * + shared_w[n] * shared_out (shared_w null: 1); rows: dtype [*, width], the experts' outputs on rows sorted by expert. */
+ * + shared_w[n] * shared_out (shared_w null: 1); rows: dtype [*, width], the experts' outputs on rows sorted by expert; wgt null:
+ * weights of 1 (experts that were fed their weighted input). */
 int mixers_moe_combine(int dtype, const void* rows, const int32_t* pos, const int32_t* idx, const float* wgt, const void* h,
                        const void* shared_out, const float* shared_w, long n_rows, int width, int top, int n_experts, int n_out, float* y,
                        mixers_stream_t stream);
+
+/* rows_in[pos[i], :] = h[i / top, :] * wgt[i] in dtype for every pair i with idx[i] < n_experts: the sorted input rows of experts
+ * that are fed their weighted input */
+int mixers_moe_scatter_scaled(int dtype, const void* h, const int32_t* pos, const int32_t* idx, const float* wgt, long n_pairs, int top,
+                              int width, int n_experts, void* rows_in, mixers_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -57,6 +57,20 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// the oldest storage index that a query at storage index c may see.  window > 0: itself and the window - 1 positions before it;
+// chunk > 0: only positions of its own chunk, chunks of `chunk` positions counted from the row's first token (storage index
+// first_real, which is negative once the row's first positions have left the storage); never anything before first_real.
+// Non-decreasing in c, so the first row of a tile bounds the tile.
+__device__ __forceinline__ int visible_from(int c, int first_real, int window, int chunk) {
+    int lo = window > 0 ? c - window + 1 : 0;
+    if (chunk > 0 && c >= first_real) {
+        const int start = first_real + (c - first_real) / chunk * chunk;
+        if (start > lo) lo = start;
+    }
+    if (lo < first_real) lo = first_real;
+    return lo < 0 ? 0 : lo;
+}
+
 #define MIXERS_DISPATCH(dtype, ...)                                                              \
     do {                                                                                         \
         if ((dtype) == 0) { using T = float; __VA_ARGS__; }                                      \

@@ -52,6 +52,14 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __re
     return warp_sum(s);
 }
 
+// a . (b * w) with the scaled b rounded to the model's type first (an expert that is fed its weighted input)
+template <typename T>
+__device__ __forceinline__ float warp_dot_scaled(const T* __restrict__ a, const T* __restrict__ b, int n, int lane, float w) {
+    float s = 0.0f;
+    for (int c = lane; c < n; c += 32) s += to_f(a[c]) * to_f(from_f<T>(to_f(b[c]) * w));
+    return warp_sum(s);
+}
+
 // one block of ROUTER_WARPS warps per token.  The rows of the product (the router's and, if given, the shared expert's gate row)
 // are cut into `split` pieces each and the pieces dealt to the warps (16-byte loads): a decoding step's lone token pays the
 // latency of one short piece, not of whole rows one after another.  Few tokens get blocks of ROUTER_WARPS warps, a prompt's many
@@ -101,7 +109,7 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32) scored_router_kernel(
     for (int e = lane; e < n_out; e += 32) {
         const float s = score_mode == 0 ? expf(score[e] - big) / sum : sigmoid_f(score[e]);
         score[e] = s;
-        choice[e] = s + to_f(correction[e]);
+        choice[e] = correction ? s + to_f(correction[e]) : s;
         blocked[e] = 1;
     }
     __syncwarp();
@@ -148,9 +156,11 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32) scored_router_kernel(
     }
 }
 
-// kind 0: silu(g) u;  kind 1: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+// kind 0: silu(g) u;  kind 1: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+// kind 2: no gate, the exact (erf) gelu of u -- the expert's first matrix then has ff rows, not 2 ff
 __device__ __forceinline__ float glu_act(float g, float u, int kind, float limit) {
     if (kind == 0) return silu_f(g) * u;
+    if (kind == 2) return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g * sigmoid_f(1.702f * g) * (u + 1.0f);
@@ -160,11 +170,13 @@ __device__ __forceinline__ float glu_act(float g, float u, int kind, float limit
 // expert, that one as slot number `top` (table entry n_experts, weight 1).  gate_up[e]: address of expert e's [2 ff_e, width]
 // matrix (gate rows first), down[e]: [width, ff_e]; ffs[e] = ff_e (null: `ff` for all).  act: [n_rows, slots, ff] scratch.
 // grid (ceil(ff / 8), n_rows * slots), 8 warps a block, one warp per row pair of the gate and up matrices:
-// act[n, k, j] = silu(gate_j . h) * (up_j . h)
+// act[n, k, j] = silu(gate_j . h) * (up_j . h).  weight_input: the token's weight for the choice multiplies the expert's INPUT
+// (rounded to the model's type) instead of its output
 template <typename T>
-__global__ void __launch_bounds__(256) moe_small_up_kernel(const T* __restrict__ h, const int32_t* __restrict__ idx, const int64_t* __restrict__ gate_up,
+__global__ void __launch_bounds__(256) moe_small_up_kernel(const T* __restrict__ h, const int32_t* __restrict__ idx, const float* __restrict__ wgt,
+                                                           const int64_t* __restrict__ gate_up,
                                                            const int32_t* __restrict__ ffs, int width, int ff, int top, int slots, int n_experts,
-                                                           int act_kind, float limit, float limit_always, T* __restrict__ act) {
+                                                           int act_kind, int weight_input, float limit, float limit_always, T* __restrict__ act) {
     const int lane = threadIdx.x & 31;
     const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
     const long nk = blockIdx.y;
@@ -177,8 +189,12 @@ __global__ void __launch_bounds__(256) moe_small_up_kernel(const T* __restrict__
     const T* w = reinterpret_cast<const T*>(gate_up[e]);
     const T* hr = h + n * width;
     // the products leave the matrix unit of the many-token path rounded to the model's type: the same rounding here
-    const float g = to_f(from_f<T>(warp_dot(w + (long)j * width, hr, width, lane)));
-    const float u = to_f(from_f<T>(warp_dot(w + ((long)ff_e + j) * width, hr, width, lane)));
+    const bool scaled = weight_input && k < top;
+    const float tw = scaled ? wgt[n * top + k] : 1.0f;
+    const long up_row = act_kind == 2 ? j : (long)ff_e + j;
+    const float g = act_kind == 2 ? 0.0f
+                  : to_f(from_f<T>(scaled ? warp_dot_scaled(w + (long)j * width, hr, width, lane, tw) : warp_dot(w + (long)j * width, hr, width, lane)));
+    const float u = to_f(from_f<T>(scaled ? warp_dot_scaled(w + up_row * width, hr, width, lane, tw) : warp_dot(w + up_row * width, hr, width, lane)));
     if (lane == 0) act[nk * ff + j] = from_f<T>(glu_act(g, u, act_kind, k < top ? limit : limit_always));
 }
 
@@ -188,7 +204,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_small_down_kernel(const T* __restrict__ act, const int32_t* __restrict__ idx, const float* __restrict__ wgt,
                                                              const int64_t* __restrict__ down, const int32_t* __restrict__ ffs, const T* __restrict__ h,
                                                              const T* __restrict__ shared_out, int width, int ff, int top, int slots, int n_experts,
-                                                             int n_out, const float* __restrict__ always_w, float* __restrict__ y) {
+                                                             int n_out, const float* __restrict__ always_w, int weight_input, float* __restrict__ y) {
     const int lane = threadIdx.x & 31;
     const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
     const long n = blockIdx.y;
@@ -196,13 +212,13 @@ __global__ void __launch_bounds__(256) moe_small_down_kernel(const T* __restrict
     float sum = 0.0f;
     for (int k = 0; k < slots; ++k) {
         const int e = k < top ? idx[n * top + k] : n_experts;
-        const float w = k < top ? wgt[n * top + k] : (always_w ? always_w[n] : 1.0f);
+        const float w = k < top ? (weight_input ? 1.0f : wgt[n * top + k]) : (always_w ? always_w[n] : 1.0f);
         if (k == top || e < n_experts) {
             const int ff_e = ffs ? ffs[e] : ff;
             const T* wd = reinterpret_cast<const T*>(down[e]);
             sum += w * to_f(from_f<T>(warp_dot(wd + (long)c * ff_e, act + (n * slots + k) * ff, ff_e, lane)));
         } else if (e < n_out) {
-            sum += w * to_f(h[n * width + c]);
+            sum += wgt[n * top + k] * to_f(h[n * width + c]);
         }
     }
     if (shared_out) sum += to_f(shared_out[n * width + c]);
@@ -234,7 +250,20 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restric
     }
 }
 
-// y[n, c] = sum_k w[n, k] * rows[pos[n, k], c] (identity experts: w * h[n, c]) + shared_w[n] * shared[n, c]
+// rows_in[pos[i], c] = h[i / top, c] * wgt[i] in the model's type, for every (token, choice) pair i that chose an expert: the
+// sorted rows of experts that are fed their weighted input
+template <typename T>
+__global__ void moe_scatter_scaled_kernel(const T* __restrict__ h, const int32_t* __restrict__ pos, const int32_t* __restrict__ idx,
+                                          const float* __restrict__ wgt, long n_pairs, int top, int width, int n_experts, T* __restrict__ rows_in) {
+    const long total = n_pairs * width;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long pr = i / width;
+        const int c = (int)(i - pr * width);
+        if (idx[pr] < n_experts) rows_in[(long)pos[pr] * width + c] = from_f<T>(to_f(h[(pr / top) * width + c]) * wgt[pr]);
+    }
+}
+
+// y[n, c] = sum_k w[n, k] * rows[pos[n, k], c] (identity experts: w * h[n, c]) + shared_w[n] * shared[n, c]; wgt null: weights of 1
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int32_t* __restrict__ pos, const int32_t* __restrict__ idx,
                                    const float* __restrict__ wgt, const T* __restrict__ h, const T* __restrict__ shared_out,
@@ -246,7 +275,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int32_t* __
         float sum = 0.0f;
         for (int k = 0; k < top; ++k) {
             const int e = idx[n * top + k];
-            const float w = wgt[n * top + k];
+            const float w = wgt ? wgt[n * top + k] : 1.0f;
             if (e < n_experts) sum += w * to_f(rows[(long)pos[n * top + k] * width + c]);
             else if (e < n_out) sum += w * to_f(h[i]);
         }
@@ -282,19 +311,21 @@ extern "C" int mixers_grouped_router(int dtype, const void* h, long n_rows, int 
 
 extern "C" int mixers_moe_small(int dtype, const void* h, long n_rows, int width, int ff, int top, int n_experts, int n_out, const int32_t* idx,
                                 const float* wgt, const int64_t* gate_up, const int64_t* down, const int32_t* ffs, int always_on,
-                                const float* always_w, int act_kind, float limit, float limit_always, const void* shared_out, void* act,
-                                float* y, mixers_stream_t stream) {
+                                const float* always_w, int act_kind, int weight_input, float limit, float limit_always, const void* shared_out,
+                                void* act, float* y, mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
+    if (act_kind < 0 || act_kind > 2) return (int)cudaErrorInvalidValue;
     const int slots = top + (always_on ? 1 : 0);
     if (n_rows * slots > 65535 || n_rows > 65535) return (int)cudaErrorInvalidValue;
     if ((n_experts > 0 || always_on) && ff > 0) {
         dim3 g1((ff + 7) / 8, (unsigned)(n_rows * slots));
-        MIXERS_DISPATCH(dtype, moe_small_up_kernel<T><<<g1, 256, 0, (cudaStream_t)stream>>>((const T*)h, idx, gate_up, ffs, width, ff, top, slots, n_experts,
-                                                                                          act_kind, limit, limit_always, (T*)act));
+        MIXERS_DISPATCH(dtype, moe_small_up_kernel<T><<<g1, 256, 0, (cudaStream_t)stream>>>((const T*)h, idx, wgt, gate_up, ffs, width, ff, top, slots,
+                                                                                          n_experts, act_kind, weight_input, limit, limit_always,
+                                                                                          (T*)act));
     }
     dim3 g2((width + 7) / 8, (unsigned)n_rows);
     MIXERS_DISPATCH(dtype, moe_small_down_kernel<T><<<g2, 256, 0, (cudaStream_t)stream>>>(
-        (const T*)act, idx, wgt, down, ffs, (const T*)h, (const T*)shared_out, width, ff, top, slots, n_experts, n_out, always_w, y));
+        (const T*)act, idx, wgt, down, ffs, (const T*)h, (const T*)shared_out, width, ff, top, slots, n_experts, n_out, always_w, weight_input, y));
     return mixers_status();
 }
 
@@ -316,5 +347,15 @@ extern "C" int mixers_moe_sort(const int32_t* idx, long n_pairs, int top, int n_
     size_t smem = 2 * (size_t)n_keys * sizeof(int);
     if (n_keys < 1 || smem > 48 * 1024 || top < 1) return (int)cudaErrorInvalidValue;
     moe_sort_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(idx, n_pairs, top, n_keys, counts, pos, token_of);
+    return mixers_status();
+}
+
+extern "C" int mixers_moe_scatter_scaled(int dtype, const void* h, const int32_t* pos, const int32_t* idx, const float* wgt, long n_pairs, int top,
+                                         int width, int n_experts, void* rows_in, mixers_stream_t stream) {
+    if (n_pairs <= 0) return 0;
+    long blocks = (n_pairs * width + 255) / 256;
+    if (blocks > 148L * 16) blocks = 148L * 16;
+    MIXERS_DISPATCH(dtype, moe_scatter_scaled_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)h, pos, idx, wgt, n_pairs, top, width,
+                                                                                                          n_experts, (T*)rows_in));
     return mixers_status();
 }

@@ -104,26 +104,61 @@ __global__ void __launch_bounds__(LN_THREADS) layer_norm_residual_kernel(float* 
     for (int c = threadIdx.x; c < width; c += LN_THREADS) out[base + c] = from_f<T>((x[base + c] - mean) * inv * to_f(w[c]));
 }
 
-// one warp per (row, head); w_head_stride: 0 = one weight vector [vdim] for every head, vdim = a vector per head [heads * vdim]
+// one warp per (row, head); w_head_stride: 0 = one weight vector [vdim] for every head, vdim = a vector per head [heads * vdim].
+// gate_mode bit 0: the gate is sigmoid(g) instead of silu(g); bit 1: the gate multiplies BEFORE the norm (the root mean square is
+// that of the gated values) instead of after it
 template <typename T>
 __global__ void gated_rms_norm_kernel(const float* __restrict__ o, long n_rows, int heads, int vdim, const T* __restrict__ gate, int ld_gate,
                                       int off_g, const T* __restrict__ w, int w_head_stride, float eps, T* __restrict__ out, int ld_out, int out_col,
-                                      float out_scale) {
+                                      float out_scale, int gate_mode) {
     long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     if (warp >= n_rows * heads) return;
     long n = warp / heads;
     int h = (int)(warp - n * heads);
     const float* src = o + warp * (long)vdim;
+    const T* g = gate + n * (long)ld_gate + off_g + h * vdim;
+    auto gated = [&](int c) { const float z = to_f(g[c]); return (gate_mode & 1) ? sigmoid_f(z) : silu_f(z); };
+    const bool first = (gate_mode & 2) != 0;
     float ss = 0.0f;
-    for (int c = lane; c < vdim; c += 32) { float v = src[c]; ss += v * v; }
+    for (int c = lane; c < vdim; c += 32) { float v = first ? src[c] * gated(c) : src[c]; ss += v * v; }
     ss = warp_sum(ss);
     float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
-    const T* g = gate + n * (long)ld_gate + off_g + h * vdim;
     T* dst = out + n * (long)ld_out + out_col + h * vdim;
     w += (long)h * w_head_stride;
     for (int c = lane; c < vdim; c += 32)
-        dst[c] = from_f<T>(src[c] * inv * to_f(w[c]) * silu_f(to_f(g[c])) * out_scale);
+        dst[c] = from_f<T>(src[c] * inv * to_f(w[c]) * gated(c) * out_scale);
+}
+
+// o[n, c] *= sigmoid(gate[n, off_g + c / per_gate]) in place: a gate per channel (per_gate 1) or one per head (per_gate = the
+// head's channels)
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ o, long n_rows, int cols, const T* __restrict__ gate, int ld_gate, int off_g, int per_gate) {
+    const long total = n_rows * cols;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long n = i / cols;
+        const int c = (int)(i - n * cols);
+        o[i] = from_f<T>(to_f(o[i]) * sigmoid_f(to_f(gate[n * ld_gate + off_g + c / per_gate])));
+    }
+}
+
+// one block per row: out = scale * (a / rms(a) * w_a + b / rms(b) * w_b), 32-bit out (two branch outputs meet as normalised vectors)
+template <typename T>
+__global__ void rms_pair_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ w_a, const T* __restrict__ w_b, float eps,
+                                    float scale, int width, float* __restrict__ out) {
+    __shared__ float red[2][32];
+    const long base = (long)blockIdx.x * width;
+    float sa = 0.0f, sb = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float u = to_f(a[base + c]), v = to_f(b[base + c]); sa += u * u; sb += v * v; }
+    sa = warp_sum(sa); sb = warp_sum(sb);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) { red[0][wid] = sa; red[1][wid] = sb; }
+    __syncthreads();
+    sa = sb = 0.0f;
+    for (int i = 0; i < nw; ++i) { sa += red[0][i]; sb += red[1][i]; }
+    const float fa = scale / sqrtf(sa / (float)width + eps), fb = scale / sqrtf(sb / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        out[base + c] = to_f(a[base + c]) * fa * to_f(w_a[c]) + to_f(b[base + c]) * fb * to_f(w_b[c]);
 }
 
 // one block per row
@@ -203,13 +238,14 @@ extern "C" int mixers_layer_norm_residual(int dtype, float* x, long n_rows, int 
 
 extern "C" int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int heads, int vdim, const void* gate, int ld_gate, int off_g,
                                      const void* w, int w_head_stride, float eps, void* out, int ld_out, int out_col, float out_scale,
-                                     mixers_stream_t stream) {
+                                     int gate_mode, mixers_stream_t stream) {
     if (n_rows <= 0) return 0;
+    if (gate_mode & ~3) return (int)cudaErrorInvalidValue;
     long warps = n_rows * heads;
     int blocks = (int)((warps + 3) / 4);
     MIXERS_DISPATCH(dtype, gated_rms_norm_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(o, n_rows, heads, vdim, (const T*)gate, ld_gate, off_g,
                                                                                                 (const T*)w, w_head_stride, eps, (T*)out, ld_out, out_col,
-                                                                                                out_scale));
+                                                                                                out_scale, gate_mode));
     return mixers_status();
 }
 
@@ -222,5 +258,23 @@ extern "C" int mixers_poly_norm(int dtype, const void* z, long n_rows, int width
 extern "C" int mixers_soft_cap(int dtype, const void* x, long n, float cap, float* out, mixers_stream_t stream) {
     if (n <= 0) return 0;
     MIXERS_DISPATCH(dtype, soft_cap_kernel<T><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((const T*)x, n, cap, out));
+    return mixers_status();
+}
+
+extern "C" int mixers_sigmoid_gate(int dtype, void* o, long n_rows, int cols, const void* gate, int ld_gate, int off_g, int per_gate,
+                                   mixers_stream_t stream) {
+    if (n_rows <= 0 || cols <= 0) return 0;
+    if (per_gate < 1) return (int)cudaErrorInvalidValue;
+    MIXERS_DISPATCH(dtype, sigmoid_gate_kernel<T><<<grid_for(n_rows * cols, 256), 256, 0, (cudaStream_t)stream>>>((T*)o, n_rows, cols, (const T*)gate,
+                                                                                                                 ld_gate, off_g, per_gate));
+    return mixers_status();
+}
+
+extern "C" int mixers_rms_pair_sum(int dtype, const void* a, const void* b, const void* w_a, const void* w_b, float eps, float scale, long n_rows,
+                                   int width, float* out, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    MIXERS_DISPATCH(dtype, rms_pair_sum_kernel<T><<<(unsigned)n_rows, threads, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)b, (const T*)w_a,
+                                                                                                        (const T*)w_b, eps, scale, width, out));
     return mixers_status();
 }

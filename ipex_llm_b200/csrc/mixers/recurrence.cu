@@ -4,6 +4,9 @@
 //   gated delta rule:        M <- g M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q
 //   gated linear attention:  M <- diag(alpha) M + k v^T;       o = M^T q
 //   wkv (RWKV-style):        o = (M + diag(u) k v^T)^T r;      M <- diag(w) M + k v^T     (w = exp(-exp(z + w0)) per key channel)
+//   channel delta rule:      M <- diag(a) M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q   (a = exp(-exp(A) softplus(z + bias))
+//                                                                                                  per key channel)
+//   state-space scan:        M <- g M + dt k v^T;              o = M^T q + D v            (g = exp(-exp(A) dt), dt = softplus(. + bias))
 // column j only needs k, q, the token's scalars and v_j.  So a column is owned by LPC lanes of a warp (LPC a power of two), each
 // holding R rows of it in registers for the whole call; tokens are taken in order.  Half of the block's warps own columns; the
 // other half stage the NEXT 16 tokens meanwhile in the second of two shared-memory buffers: their k / q (/ alpha) rows, scalars
@@ -16,10 +19,11 @@
 #include "mixers_common.cuh"
 
 // one block row per token (blockIdx.x), channels across the block and blockIdx.y: no index division in the loop
+// flags: bit 0 = silu on the result, bit 1 = the current token's input is added to the result (y = x + conv(x)); bias may be null
 template <typename T>
-__global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S, int ld, int off, int C, int taps, const T* __restrict__ w,
-                                       const T* __restrict__ tail, T* __restrict__ tail_next, int slot0, const int32_t* __restrict__ pad,
-                                       T* __restrict__ y) {
+__global__ void short_conv_kernel(const T* __restrict__ proj, int B, int S, int ld, int off, int C, int taps, const T* __restrict__ w,
+                                  const T* __restrict__ bias, int flags, const T* __restrict__ tail, T* __restrict__ tail_next, int slot0,
+                                  const int32_t* __restrict__ pad, T* __restrict__ y) {
     const int tl = taps - 1 > 0 ? taps - 1 : 1;             // rows of a tail buffer
     const int n = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -34,9 +38,11 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ proj, int B, int S,
         if (tt < first) return 0.0f;
         return to_f(in[(long)tt * ld]);
     };
-    float acc = 0.0f;
+    float acc = bias ? to_f(bias[c]) : 0.0f;
     for (int j = 0; j < taps; ++j) acc += to_f(w[(long)c * taps + j]) * input(t - (taps - 1) + j);
-    y[(long)n * C + c] = from_f<T>(t < first ? 0.0f : silu_f(acc));
+    if (flags & 1) acc = silu_f(acc);
+    if (flags & 2) acc += input(t);
+    y[(long)n * C + c] = from_f<T>(t < first ? 0.0f : acc);
     if (t == S - 1)
         for (int r = 0; r < taps - 1; ++r) tail_next[((long)b * tl + r) * C + c] = from_f<T>(input(S - (taps - 1) + r));
 }
@@ -67,6 +73,9 @@ constexpr int REC_THREADS = REC_CONSUMERS + REC_PRODUCERS;
 constexpr int REC_TPW = 4;                                  // tokens a producer warp stages at a time
 constexpr int REC_TC = REC_TPW * (REC_PRODUCERS / 32);      // tokens per stage (16)
 
+// which modes stage a row of decays per token (one per key channel) beside k and q
+__host__ __device__ constexpr bool rec_decay_rows(int mode) { return mode == 1 || mode == 2 || mode == 3; }
+
 struct RecArgs {
     const void* src;        // delta: conv output [B, S, C]; gla: projection [B, S, ld]
     int ld_src;
@@ -77,10 +86,10 @@ struct RecArgs {
     int ld_proj, off_b, off_a;
     const void* A_log;
     const void* dt_bias;
-    const void* z;          // gla, wkv: decay logits [B, S, heads * dim]
+    const void* z;          // gla, wkv, channel delta: decay logits [B, S, heads * dim]
     float inv_tau;
-    const void* w0;         // wkv: added to the decay logits [heads * dim]
-    const void* u;          // wkv: the current token's bonus [heads * dim]
+    const void* w0;         // wkv, channel delta: added to the decay logits [heads * dim]
+    const void* u;          // wkv: the current token's bonus [heads * dim]; state-space scan: the skip weight D [heads]
     int B, S, heads, dim, vdim, slot0;
     const int32_t* pad;
     float* state;
@@ -93,9 +102,9 @@ template <int MODE>
 struct RecStage {
     float *k, *q, *a, *v, *sc;
     __device__ RecStage(float* base, int tc, int dp, int cols_blk) {
-        k = base; q = k + tc * dp; a = q + tc * dp; v = a + (MODE != 0 ? tc * dp : 0); sc = v + tc * cols_blk;
+        k = base; q = k + tc * dp; a = q + tc * dp; v = a + (rec_decay_rows(MODE) ? tc * dp : 0); sc = v + tc * cols_blk;
     }
-    static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((MODE != 0 ? 3 : 2) * dp + cols_blk + 4); }
+    static __host__ __device__ size_t floats(int tc, int dp, int cols_blk) { return (size_t)tc * ((rec_decay_rows(MODE) ? 3 : 2) * dp + cols_blk + 4); }
 };
 
 // producers: tokens t0 .. t0 + nt - 1 of the call into one stage.  A warp takes up to REC_TPW tokens at once, and EVERY global
@@ -125,10 +134,10 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
         }
     }
     float lb = 0.0f, la = 0.0f;                              // lane j: the gate logits of the warp's token j
-    if (MODE == 0 && lane < cnt) {
+    if ((MODE == 0 || MODE == 3 || MODE == 4) && lane < cnt) {
         const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt0 + lane) * a.ld_proj;
-        lb = to_f(pr[a.off_b + h]);
-        la = to_f(pr[a.off_a + h]);
+        if (MODE != 4) lb = to_f(pr[a.off_b + h]);
+        if (MODE != 3) la = to_f(pr[a.off_a + h]);
     }
     if (cnt > 0) {
         float sq[REC_TPW], sk[REC_TPW], skq[REC_TPW];
@@ -136,25 +145,25 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
         for (int j = 0; j < REC_TPW; ++j) sq[j] = sk[j] = skq[j] = 0.0f;
         for (int blk = 0; blk < dp; blk += 128) {
             float qv[REC_TPW][4], kv[REC_TPW][4], zv[REC_TPW][4], w0v[4], uv[4];
-            if (MODE == 2) {
+            if (MODE == 2 || MODE == 3) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = blk + lane + 32 * e;
                     w0v[e] = i < dim ? to_f(((const T*)a.w0)[h * dim + i]) : 0.0f;
-                    uv[e] = i < dim ? to_f(((const T*)a.u)[h * dim + i]) : 0.0f;
+                    if (MODE == 2) uv[e] = i < dim ? to_f(((const T*)a.u)[h * dim + i]) : 0.0f;
                 }
             }
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) {
                 const T* row = src + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * a.ld_src;
-                const T* zr = MODE != 0 ? (const T*)a.z + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * ((long)a.heads * dim) + h * dim : nullptr;
+                const T* zr = rec_decay_rows(MODE) ? (const T*)a.z + ((long)b * S + t0 + tt0 + (j < cnt ? j : 0)) * ((long)a.heads * dim) + h * dim : nullptr;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = blk + lane + 32 * e;
                     const bool ok = j < cnt && i < dim;
                     qv[j][e] = ok ? to_f(row[a.off_q + qh * dim + i]) : 0.0f;
                     kv[j][e] = ok ? to_f(row[a.off_k + qh * dim + i]) : 0.0f;
-                    if (MODE != 0) zv[j][e] = ok ? to_f(zr[i]) : 0.0f;
+                    if (rec_decay_rows(MODE)) zv[j][e] = ok ? to_f(zr[i]) : 0.0f;
                 }
             }
 #pragma unroll
@@ -171,7 +180,10 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
                                 st.a[(tt0 + j) * dp + i] = i < dim ? expf(-expf(zv[j][e] + w0v[e])) : 1.0f;
                                 st.q[(tt0 + j) * dp + i] = qv[j][e];
                                 skq[j] += qv[j][e] * uv[e] * kv[j][e];
+                            } else if (MODE == 4) {
+                                st.q[(tt0 + j) * dp + i] = qv[j][e];
                             } else {
+                                if (MODE == 3) st.a[(tt0 + j) * dp + i] = i < dim ? expf(neg_exp_a * softplus_f(zv[j][e] + w0v[e])) : 1.0f;
                                 st.q[(tt0 + j) * dp + i] = qv[j][e];
                                 sq[j] += qv[j][e] * qv[j][e]; sk[j] += kv[j][e] * kv[j][e]; skq[j] += qv[j][e] * kv[j][e];
                             }
@@ -181,7 +193,7 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
                 }
             }
         }
-        if (MODE == 0) {
+        if (MODE == 0 || MODE == 3) {
 #pragma unroll
             for (int j = 0; j < REC_TPW; ++j) { sq[j] = warp_sum(sq[j]); sk[j] = warp_sum(sk[j]); skq[j] = warp_sum(skq[j]); }
             __syncwarp();
@@ -195,10 +207,15 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
                 }
             }
             if (lane < cnt) {
-                st.sc[(tt0 + lane) * 4 + 0] = expf(neg_exp_a * softplus_f(la + dt_bias));
+                st.sc[(tt0 + lane) * 4 + 0] = MODE == 0 ? expf(neg_exp_a * softplus_f(la + dt_bias)) : 1.0f;
                 st.sc[(tt0 + lane) * 4 + 1] = sigmoid_f(lb);
                 st.sc[(tt0 + lane) * 4 + 2] = my_kq * my_nq * my_nk;
             }
+        }
+        if (MODE == 4 && lane < cnt) {
+            const float dt = softplus_f(la + dt_bias);
+            st.sc[(tt0 + lane) * 4 + 0] = expf(neg_exp_a * dt);
+            st.sc[(tt0 + lane) * 4 + 1] = dt;
         }
         if (MODE == 2) {
             float mine = 0.0f;
@@ -222,7 +239,8 @@ __device__ __forceinline__ void rec_stage_tokens(const RecArgs& a, RecStage<MODE
 // one block per SM: what counts is how fast ONE block walks its tokens; demanding 1 explicitly made it take more registers and
 // run 10 % slower); 2 halves them (some spills) so that two blocks hide each other's latencies, which pays when the grid has
 // more blocks than the GPU has SMs (batches, many heads): measured for the wkv mode only.
-template <typename T, int MODE, int R, int MINB>           // MODE 0: gated delta rule, 1: gated linear attention, 2: wkv
+template <typename T, int MODE, int R, int MINB>           // MODE 0: gated delta rule, 1: gated linear attention, 2: wkv,
+                                                           // 3: channel delta rule, 4: state-space scan
 __global__ void __launch_bounds__(REC_THREADS, MINB) linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sh[];
     const int lpc = a.lpc, dp = R * lpc, tc = a.tc;
@@ -255,10 +273,11 @@ __global__ void __launch_bounds__(REC_THREADS, MINB) linear_recurrence_kernel(Re
 
     const int nchunks = (S - first + tc - 1) / tc;
     float neg_exp_a = 0.0f, dt_bias = 0.0f;
-    if (MODE == 0 && producer) {
+    if ((MODE == 0 || MODE == 3 || MODE == 4) && producer) {
         neg_exp_a = -expf(to_f(((const T*)a.A_log)[h]));
-        dt_bias = to_f(((const T*)a.dt_bias)[h]);
+        if (MODE != 3) dt_bias = to_f(((const T*)a.dt_bias)[h]);
     }
+    const float skip = (MODE == 4 && !producer) ? to_f(((const T*)a.u)[h]) : 0.0f;
     if (producer && nchunks > 0)
         rec_stage_tokens<T, MODE>(a, RecStage<MODE>(sh, tc, dp, cols_blk), b, h, qh, first, (S - first < tc ? S - first : tc), dp, cols_blk, col0,
                                   tid - REC_CONSUMERS, neg_exp_a, dt_bias);
@@ -297,6 +316,26 @@ __global__ void __launch_bounds__(REC_THREADS, MINB) linear_recurrence_kernel(Re
                     o = g * cqs + kq * u;
 #pragma unroll
                     for (int r = 0; r < R; ++r) M[r] += kr[r] * u;
+                } else if (MODE == 3) {
+                    const float* aa = st.a + tt * dp + sub;
+                    const float beta = st.sc[tt * 4 + 1], kq = st.sc[tt * 4 + 2];
+                    float ak[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { M[r] *= aa[r * lpc]; ak[r & 3] += M[r] * kr[r]; cq[r & 3] += M[r] * qr[r]; }
+                    float aks = (ak[0] + ak[1]) + (ak[2] + ak[3]), cqs = (cq[0] + cq[1]) + (cq[2] + cq[3]);
+                    for (int m = lpc >> 1; m > 0; m >>= 1) { aks += __shfl_xor_sync(0xffffffffu, aks, m); cqs += __shfl_xor_sync(0xffffffffu, cqs, m); }
+                    const float u = beta * (v - aks);
+                    o = cqs + kq * u;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) M[r] += kr[r] * u;
+                } else if (MODE == 4) {
+                    const float g = st.sc[tt * 4 + 0], dv = st.sc[tt * 4 + 1] * v;
+                    float op[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < R; ++r) { M[r] = g * M[r] + kr[r] * dv; op[r & 3] += M[r] * qr[r]; }
+                    o = (op[0] + op[1]) + (op[2] + op[3]);
+                    for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                    o += skip * v;
                 } else if (MODE == 1) {
                     const float* aa = st.a + tt * dp + sub;
                     float op[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -340,7 +379,7 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
     float* kbuf = sh;                                        // [tc][dp]
     float* qbuf = kbuf + tc * dp;                            // [tc][dp]
     float* abuf = qbuf + tc * dp;                            // [tc][dp] (gla, wkv)
-    float* vbuf = abuf + (MODE != 0 ? tc * dp : 0);          // [tc][cols_blk]
+    float* vbuf = abuf + (rec_decay_rows(MODE) ? tc * dp : 0);   // [tc][cols_blk]
     float* sc = vbuf + tc * cols_blk;                        // [tc][4]: g, beta, k.q (wkv: [2] = sum r u k)
     const int b = blockIdx.z, h = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -366,6 +405,7 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
     if (sub == 0 && col_ok)
         for (int t = 0; t < first; ++t) obase[(long)t * a.heads * vdim + col] = 0.0f;
     const float q_scale = rsqrtf((float)dim);
+    const float skip = MODE == 4 ? to_f(((const T*)a.u)[h]) : 0.0f;
 
     for (int t0 = first; t0 < S; t0 += tc) {
         const int nt = S - t0 < tc ? S - t0 : tc;
@@ -382,18 +422,33 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
                 kbuf[tt * dp + i] = kv;
                 sq += qv * qv; sk += kv * kv; skq += qv * kv;
             }
-            if (MODE == 0) {
+            if (MODE == 0 || MODE == 3) {
                 sq = warp_sum(sq); sk = warp_sum(sk); skq = warp_sum(skq);
                 const float nq = q_scale / sqrtf(sq + 1e-6f), nk = 1.0f / sqrtf(sk + 1e-6f);
                 __syncwarp();
                 for (int i = lane; i < dp; i += 32) { qbuf[tt * dp + i] *= nq; kbuf[tt * dp + i] *= nk; }
+                if (MODE == 3) {
+                    const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
+                    const T* w0 = (const T*)a.w0 + h * dim;
+                    const float neg_exp_a = -expf(to_f(((const T*)a.A_log)[h]));
+                    for (int i = lane; i < dp; i += 32) abuf[tt * dp + i] = i < dim ? expf(neg_exp_a * softplus_f(to_f(zr[i]) + to_f(w0[i]))) : 1.0f;
+                }
                 if (lane == 0) {
                     const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt) * a.ld_proj;
                     float beta = sigmoid_f(to_f(pr[a.off_b + h]));
-                    float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
-                    sc[tt * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
+                    if (MODE == 0) {
+                        float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
+                        sc[tt * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
+                    }
                     sc[tt * 4 + 1] = beta;
                     sc[tt * 4 + 2] = skq * nq * nk;
+                }
+            } else if (MODE == 4) {
+                if (lane == 0) {
+                    const T* pr = (const T*)a.proj + ((long)b * S + t0 + tt) * a.ld_proj;
+                    const float dt = softplus_f(to_f(pr[a.off_a + h]) + to_f(((const T*)a.dt_bias)[h]));
+                    sc[tt * 4 + 0] = expf(-expf(to_f(((const T*)a.A_log)[h])) * dt);
+                    sc[tt * 4 + 1] = dt;
                 }
             } else if (MODE == 1) {
                 const T* zr = (const T*)a.z + ((long)b * S + t0 + tt) * ((long)a.heads * dim) + h * dim;
@@ -436,6 +491,23 @@ __global__ void __launch_bounds__(REC_FEW_THREADS) linear_recurrence_few_kernel(
                 o = g * cq + kq * u;
 #pragma unroll
                 for (int r = 0; r < R; ++r) M[r] = g * M[r] + kk[r * lpc] * u;
+            } else if (MODE == 3) {
+                const float* aa = abuf + tt * dp + sub;
+                float ak = 0.0f, cq = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { M[r] *= aa[r * lpc]; ak += M[r] * kk[r * lpc]; cq += M[r] * qq[r * lpc]; }
+                for (int m = lpc >> 1; m > 0; m >>= 1) { ak += __shfl_xor_sync(0xffffffffu, ak, m); cq += __shfl_xor_sync(0xffffffffu, cq, m); }
+                const float u = sc[tt * 4 + 1] * (v - ak);
+                o = cq + sc[tt * 4 + 2] * u;
+#pragma unroll
+                for (int r = 0; r < R; ++r) M[r] += kk[r * lpc] * u;
+            } else if (MODE == 4) {
+                const float g = sc[tt * 4 + 0], dv = sc[tt * 4 + 1] * v;
+                o = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { M[r] = g * M[r] + kk[r * lpc] * dv; o += M[r] * qq[r * lpc]; }
+                for (int m = lpc >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                o += skip * v;
             } else if (MODE == 1) {
                 const float* aa = abuf + tt * dp + sub;
                 o = 0.0f;
@@ -471,7 +543,7 @@ static int launch_recurrence_few(RecArgs a, cudaStream_t stream) {
     while (lpc < need) lpc <<= 1;
     if (lpc > 32) return (int)cudaErrorInvalidValue;
     int dp = r * lpc, cols_blk = REC_FEW_THREADS / lpc;
-    int arrays = MODE != 0 ? 3 : 2;
+    int arrays = rec_decay_rows(MODE) ? 3 : 2;
     int tc = a.S < REC_TC ? a.S : REC_TC;
     auto bytes = [&](int n) { return (size_t)n * (arrays * dp + cols_blk + 4) * sizeof(float); };
     while (tc > 1 && bytes(tc) > 40 * 1024) tc >>= 1;
@@ -510,15 +582,21 @@ static int launch_recurrence(RecArgs a, cudaStream_t stream) {
     return mixers_status();
 }
 
-extern "C" int mixers_short_conv_silu(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w,
-                                      const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream) {
+extern "C" int mixers_short_conv(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w, const void* bias,
+                                 int flags, const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream) {
     if (B <= 0 || S <= 0) return 0;
-    if (taps < 1) return (int)cudaErrorInvalidValue;
+    if (taps < 1 || (flags & ~3)) return (int)cudaErrorInvalidValue;
     const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
     dim3 blocks((unsigned)((long)B * S), (unsigned)((C + threads - 1) / threads));
-    MIXERS_DISPATCH(dtype, short_conv_silu_kernel<T><<<blocks, threads, 0, (cudaStream_t)stream>>>((const T*)proj, B, S, ld, off, C, taps, (const T*)w,
-                                                                                                 (const T*)tail, (T*)tail_next, slot0, pad, (T*)y));
+    MIXERS_DISPATCH(dtype, short_conv_kernel<T><<<blocks, threads, 0, (cudaStream_t)stream>>>((const T*)proj, B, S, ld, off, C, taps, (const T*)w,
+                                                                                            (const T*)bias, flags, (const T*)tail, (T*)tail_next, slot0,
+                                                                                            pad, (T*)y));
     return mixers_status();
+}
+
+extern "C" int mixers_short_conv_silu(int dtype, const void* proj, int B, int S, int ld, int off, int C, int taps, const void* w,
+                                      const void* tail, void* tail_next, int slot0, const int32_t* pad, void* y, mixers_stream_t stream) {
+    return mixers_short_conv(dtype, proj, B, S, ld, off, C, taps, w, nullptr, 1, tail, tail_next, slot0, pad, y, stream);
 }
 
 extern "C" int mixers_token_shift_mix(int dtype, const void* h, int B, int S, int C, const void* mu, int n_mix, const void* tail, void* tail_next,
@@ -566,5 +644,33 @@ extern "C" int mixers_wkv(int dtype, const void* r, const void* k, const void* v
     a.q_heads = heads; a.z = z; a.w0 = w0; a.u = u;
     a.B = B; a.S = S; a.heads = heads; a.dim = dim; a.vdim = dim; a.slot0 = slot0; a.pad = pad; a.state = state; a.o = o;
     MIXERS_DISPATCH(dtype, return (launch_recurrence<T, 2>(a, (cudaStream_t)stream)));
+    return 0;
+}
+
+extern "C" int mixers_channel_delta_rule(int dtype, const void* conv, int B, int S, int kv_heads, int heads, int dim, int vdim, const void* proj,
+                                         int ld, int off_b, const void* z, const void* A_log, const void* dt_bias, float* state, int slot0,
+                                         const int32_t* pad, float* o, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    if (kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
+    RecArgs a = {};
+    a.src = conv; a.ld_src = 2 * kv_heads * dim + heads * vdim;
+    a.off_q = 0; a.off_k = kv_heads * dim; a.off_v = 2 * kv_heads * dim; a.q_heads = kv_heads;
+    a.proj = proj; a.ld_proj = ld; a.off_b = off_b; a.z = z; a.A_log = A_log; a.w0 = dt_bias;
+    a.B = B; a.S = S; a.heads = heads; a.dim = dim; a.vdim = vdim; a.slot0 = slot0; a.pad = pad; a.state = state; a.o = o;
+    MIXERS_DISPATCH(dtype, return (launch_recurrence<T, 3>(a, (cudaStream_t)stream)));
+    return 0;
+}
+
+extern "C" int mixers_state_space_scan(int dtype, const void* conv, int B, int S, int groups, int heads, int n_state, int vdim, const void* proj,
+                                       int ld, int off_dt, const void* A_log, const void* dt_bias, const void* skip, float* state, int slot0,
+                                       const int32_t* pad, float* o, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    if (groups < 1 || heads % groups != 0) return (int)cudaErrorInvalidValue;
+    RecArgs a = {};
+    a.src = conv; a.ld_src = heads * vdim + 2 * groups * n_state;
+    a.off_v = 0; a.off_k = heads * vdim; a.off_q = heads * vdim + groups * n_state; a.q_heads = groups;
+    a.proj = proj; a.ld_proj = ld; a.off_a = off_dt; a.A_log = A_log; a.dt_bias = dt_bias; a.u = skip;
+    a.B = B; a.S = S; a.heads = heads; a.dim = n_state; a.vdim = vdim; a.slot0 = slot0; a.pad = pad; a.state = state; a.o = o;
+    MIXERS_DISPATCH(dtype, return (launch_recurrence<T, 4>(a, (cudaStream_t)stream)));
     return 0;
 }

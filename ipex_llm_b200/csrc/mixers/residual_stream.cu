@@ -136,6 +136,122 @@ __global__ void rms_residual_cached_kernel(float* __restrict__ x, const TY* __re
     }
 }
 
+// one block per row of a stream whose sublayers run side by side on two scalar-gain RMS norms of the same x:
+//   x += y_a + y_c + y_b + y_d (each may be null; y_a, y_c in the model's type, y_b, y_d 32-bit);
+//   pre_gain: x <- x / rms(x) * pre_gain[0] first (the norm behind an embedding);
+//   stack: the new x is kept as stream `index`, and with coef replaced by sum_{j <= index} coef[j] * stack[j];
+//   h1 = x / rms(x) * gain1[0], h2 = x / rms(x) * gain2[0] (either may be null): one root mean square serves both.
+// CACHED: the row's elements stay in registers (rows up to SN_MAXC x blockDim wide), every load issued before the first reduction.
+constexpr int SN_MAXC = 8;
+template <typename T, bool CACHED>
+__global__ void sum_residual_norms_kernel(float* __restrict__ x, int width, const T* __restrict__ y_a, const T* __restrict__ y_c,
+                                          const float* __restrict__ y_b, const float* __restrict__ y_d, const T* __restrict__ pre_gain, float eps,
+                                          float* __restrict__ stack, long stack_stride, int index, const T* __restrict__ coef,
+                                          const T* __restrict__ gain1, const T* __restrict__ gain2, T* __restrict__ h1, T* __restrict__ h2) {
+    __shared__ float red[32];
+    const long base = (long)blockIdx.x * width;
+    const bool want = h1 || h2;
+    const float last = coef ? to_f(coef[index]) : 1.0f;
+    auto summed = [&](long i) {
+        float v = x[i];
+        if (y_a) v += to_f(y_a[i]);
+        if (y_c) v += to_f(y_c[i]);
+        if (y_b) v += y_b[i];
+        if (y_d) v += y_d[i];
+        return v;
+    };
+    if (CACHED) {
+        float v[SN_MAXC], av[SN_MAXC];
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < SN_MAXC; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            v[k] = c < width ? summed(base + c) : 0.0f;
+            av[k] = 0.0f;
+            ss += v[k] * v[k];
+        }
+        if (coef) {
+            for (int j = 0; j < index; ++j) {
+                const float cj = to_f(coef[j]);
+                const float* sj = stack + j * stack_stride + base;
+#pragma unroll
+                for (int k = 0; k < SN_MAXC; ++k) {
+                    const int c = threadIdx.x + k * blockDim.x;
+                    if (c < width) av[k] += cj * sj[c];
+                }
+            }
+        }
+        if (pre_gain) {
+            const float f = to_f(pre_gain[0]) / sqrtf(block_sum(ss, red) / (float)width + eps);
+#pragma unroll
+            for (int k = 0; k < SN_MAXC; ++k) v[k] *= f;
+        }
+        ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < SN_MAXC; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < width) {
+                if (stack) {
+                    stack[index * stack_stride + base + c] = v[k];
+                    if (coef) v[k] = av[k] + last * v[k];
+                }
+                x[base + c] = v[k];
+            }
+            ss += v[k] * v[k];
+        }
+        if (!want) return;
+        const float f = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+        const float f1 = h1 ? f * to_f(gain1[0]) : 0.0f, f2 = h2 ? f * to_f(gain2[0]) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < SN_MAXC; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < width) {
+                if (h1) h1[base + c] = from_f<T>(v[k] * f1);
+                if (h2) h2[base + c] = from_f<T>(v[k] * f2);
+            }
+        }
+        return;
+    }
+    // every thread re-reads only what it wrote itself
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = summed(base + c); x[base + c] = v; ss += v * v; }
+    const float f0 = pre_gain ? to_f(pre_gain[0]) / sqrtf(block_sum(ss, red) / (float)width + eps) : 1.0f;
+    if (pre_gain || stack) {
+        ss = 0.0f;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            const long i = base + c;
+            float v = x[i] * f0;
+            if (stack) {
+                stack[index * stack_stride + i] = v;
+                if (coef) {
+                    float a = 0.0f;
+                    for (int j = 0; j < index; ++j) a += to_f(coef[j]) * stack[j * stack_stride + i];
+                    v = a + last * v;
+                }
+            }
+            x[i] = v;
+            ss += v * v;
+        }
+    }
+    if (!want) return;
+    const float f = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    const float f1 = h1 ? f * to_f(gain1[0]) : 0.0f, f2 = h2 ? f * to_f(gain2[0]) : 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = x[base + c];
+        if (h1) h1[base + c] = from_f<T>(v * f1);
+        if (h2) h2[base + c] = from_f<T>(v * f2);
+    }
+}
+
+// out[n, c] = gelu(in[n, c]) with the exact (erf) form
+template <typename T>
+__global__ void gelu_erf_kernel(const T* __restrict__ in, long n, T* __restrict__ out) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float v = to_f(in[i]);
+        out[i] = from_f<T>(0.5f * v * (1.0f + erff(v * 0.7071067811865476f)));
+    }
+}
+
 // one block per row: out = x / rms(x) * gain * vec
 template <typename T>
 __global__ void rms_norm_rows_kernel(const float* __restrict__ x, const T* __restrict__ gain, const T* __restrict__ vec, float eps, int width,
@@ -278,5 +394,30 @@ extern "C" int mixers_clamped_glu(int dtype, const void* in, long n_rows, int ld
     if (n_rows <= 0 || cols <= 0) return 0;
     MIXERS_DISPATCH(dtype, clamped_glu_kernel<T><<<grid_for(n_rows * cols), 256, 0, (cudaStream_t)stream>>>((const T*)in, n_rows, ld, off_gate, off_up, cols,
                                                                                                           limit, (T*)out));
+    return mixers_status();
+}
+
+extern "C" int mixers_sum_residual_norms(int dtype, float* x, long n_rows, int width, const void* y_a, const void* y_c, const float* y_b,
+                                         const float* y_d, const void* pre_gain, float eps, float* stack, long stack_stride, int index,
+                                         const void* coef, const void* gain1, const void* gain2, void* h1, void* h2, mixers_stream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((coef && !stack) || (h1 && !gain1) || (h2 && !gain2)) return (int)cudaErrorInvalidValue;
+    int threads = width > 1024 ? 256 : 128;
+    if (n_rows <= 64)                                        // a decoding step's few rows: one round trip to memory for rows up to 8192 wide
+        while (threads < 1024 && threads * SN_MAXC < width) threads <<= 1;
+    // many rows under a depth average stream better from the plain loop
+    const bool cached = width <= SN_MAXC * threads && (n_rows <= 1024 || !coef);
+#define SN_LAUNCH(C) MIXERS_DISPATCH(dtype, sum_residual_norms_kernel<T, C><<<(unsigned)n_rows, threads, 0, (cudaStream_t)stream>>>(                    \
+        x, width, (const T*)y_a, (const T*)y_c, y_b, y_d, (const T*)pre_gain, eps, stack, stack_stride, index, (const T*)coef, (const T*)gain1, \
+        (const T*)gain2, (T*)h1, (T*)h2))
+    if (cached) SN_LAUNCH(true);
+    else SN_LAUNCH(false);
+#undef SN_LAUNCH
+    return mixers_status();
+}
+
+extern "C" int mixers_gelu_erf(int dtype, const void* in, long n, void* out, mixers_stream_t stream) {
+    if (n <= 0) return 0;
+    MIXERS_DISPATCH(dtype, gelu_erf_kernel<T><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const T*)in, n, (T*)out));
     return mixers_status();
 }

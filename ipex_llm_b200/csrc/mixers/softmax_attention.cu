@@ -5,7 +5,8 @@
 //     [batch, position, kv head, channel] tensors given by three strides each, so the same kernels serve keys / values
 //     expanded from the latent (one row per head) and the latent cache itself read as one shared key = value head of
 //     kv_rank channels (the "absorbed" form: the query carries the key expansion, the value expansion follows the sum).
-//   An optional window limits how far back a query looks (0 = every earlier position); scores may be soft-capped
+//   An optional window limits how far back a query looks (0 = every earlier position), optional chunks confine a query to the
+//   earlier positions of its own chunk (chunks counted from the row's first token); scores may be soft-capped
 //   (cap * tanh(score / cap)) and the softmax's denominator may hold a per-head sink exp(sink_h) that has no key and no value.
 //   wide_qkv_prepare: RMS norm over a token's WHOLE query projection and whole key projection (all heads at once, one weight per
 //     channel), values optionally blended with another layer's values of the same token; keys and values are appended to the
@@ -134,6 +135,68 @@ __global__ void __launch_bounds__(QP_THREADS) wide_qkv_prepare_kernel(
     }
 }
 
+// Rotary positions on the queries and keys of new tokens, taken from the columns of one projection output, with the cache write
+// of keys and values: one warp per (token, head slot) -- `heads` query heads of q_dim channels, `kv_heads` key heads of k_dim
+// channels and, when vdim > 0, `kv_heads` value heads.  Inside a head, channel rot_off + i is paired with channel
+// rot_off + i + rot_dims / 2 (i < rot_dims / 2) and the pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a) * amp with
+// a = position * inv_freq[i], the angle and its sine / cosine in double precision; the other channels pass unchanged.  The first
+// k_norm_cols channels of a key head are first divided by their root mean square and multiplied by k_norm_w (a latent that
+// shares its cache row with a rotated part).  Keys and values go to storage index held + t of caches given by three strides.
+template <typename T>
+__global__ void rope_qk_prepare_kernel(const T* __restrict__ proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
+                                       int q_dim, int k_dim, int vdim, int q_rot_off, int k_rot_off, int rot_dims, const double* __restrict__ inv_freq,
+                                       float amp, const T* __restrict__ k_norm_w, int k_norm_cols, float eps, T* __restrict__ q_out,
+                                       T* __restrict__ k_store, long k_bs, long k_ps, long k_hs, T* __restrict__ v_store, long v_bs, long v_ps,
+                                       long v_hs, int held, int shift, const int32_t* __restrict__ pad, const int32_t* __restrict__ dyn) {
+    if (dyn) held = dyn[0];
+    const int slots = heads + kv_heads + (vdim > 0 ? kv_heads : 0);
+    const long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long)B * S * slots) return;
+    const long n = warp / slots;
+    const int hs = (int)(warp - n * slots);
+    const int b = (int)(n / S), t = (int)(n - (long)b * S);
+    const int pos = held + t + shift - pad[b];              // negative: a padding slot
+    const T* row = proj + n * (long)ld;
+    if (hs >= heads + kv_heads) {
+        const int g = hs - heads - kv_heads;
+        const T* src = row + off_v + g * vdim;
+        T* dst = v_store + b * v_bs + (long)(held + t) * v_ps + g * v_hs;
+        for (int c = lane; c < vdim; c += 32) dst[c] = pos >= 0 ? src[c] : from_f<T>(0.0f);
+        return;
+    }
+    const bool is_q = hs < heads;
+    const int g = is_q ? hs : hs - heads;
+    const int dim = is_q ? q_dim : k_dim, rot_off = is_q ? q_rot_off : k_rot_off;
+    const T* src = row + (is_q ? off_q : off_k) + g * dim;
+    T* dst = is_q ? q_out + (n * heads + g) * (long)dim : k_store + b * k_bs + (long)(held + t) * k_ps + g * k_hs;
+    const int ncols = (!is_q && k_norm_w) ? k_norm_cols : 0;
+    float inv = 1.0f;
+    if (ncols > 0) {
+        float ss = 0.0f;
+        for (int c = lane; c < ncols; c += 32) { const float v = to_f(src[c]); ss += v * v; }
+        inv = 1.0f / sqrtf(warp_sum(ss) / (float)ncols + eps);
+    }
+    const int half = rot_dims >> 1;
+    const double dpos = (double)pos;
+    for (int c = lane; c < dim; c += 32) {
+        const int r = c - rot_off;
+        float y;
+        if (r >= 0 && r < rot_dims) {
+            const int i = r < half ? r : r - half;
+            double dsn, dcs;
+            sincos(dpos * inv_freq[i], &dsn, &dcs);
+            const float sn = (float)dsn * amp, cs = (float)dcs * amp;
+            const float u = to_f(src[rot_off + i]), v = to_f(src[rot_off + i + half]);
+            y = r < half ? u * cs - v * sn : v * cs + u * sn;
+        } else {
+            y = to_f(src[c]);
+            if (c < ncols) y = y * inv * to_f(k_norm_w[c]);
+        }
+        dst[c] = from_f<T>(pos >= 0 ? y : 0.0f);
+    }
+}
+
 // ---- the general kernel: any sizes and strides, any dtype, 32-bit arithmetic throughout (float32 models, decoding, short
 // portions).  A block of SA_WARPS warps per (token, query head); the warps take the visible keys in turns of 32, each with its
 // own running maximum, sum and weighted values; the warps' partial results are merged in shared memory in warp order.
@@ -151,7 +214,7 @@ __device__ __forceinline__ float dot_strided(const float* __restrict__ qs, const
 template <typename T>
 __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
-        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window, int chunk,
         float scale, float softcap, const T* __restrict__ sink, T* __restrict__ out, long ld_out, int out_col, const int32_t* __restrict__ dyn, int aligned) {
     extern __shared__ __align__(16) float sa_sh[];          // q [dim rounded up to 4], warp maxima, warp sums, partial values
     const int dim4 = (dim + 3) & ~3;
@@ -173,9 +236,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attention_kernel(
         for (int col = threadIdx.x; col < vdim; col += blockDim.x) dst[col] = from_f<T>(0.0f);
         return;
     }
-    int lo = window > 0 ? c - window + 1 : 0;
-    if (lo < first_real) lo = first_real;
-    if (lo < 0) lo = 0;
+    const int lo = visible_from(c, first_real, window, chunk);
     const T* qsrc = q + n * q_ld + h * q_hs;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) qs[d] = to_f(qsrc[d]);
     __syncthreads();
@@ -276,7 +337,7 @@ __device__ __forceinline__ float fast_cap(float s, float cap, float inv_cap) {
 template <typename T, int KDMAX, int NDMAX>                // dim <= 16 KDMAX, vdim <= 8 NDMAX; both multiples of 16
 __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
-        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* __restrict__ pad, int window, int chunk,
         float scale, float softcap, const T* __restrict__ sink, T* __restrict__ out, long ld_out, int out_col) {
     extern __shared__ __align__(16) unsigned char sa_tc_sh[];
     const int kstride = dim + 8, vstride = vdim + 8;        // elements
@@ -289,23 +350,18 @@ __global__ void __launch_bounds__(128) softmax_attention_tc_kernel(
     const int first_real = pad[b] - shift;
     const int t_last = (t0 + SA_ROWS - 1 < S - 1) ? t0 + SA_ROWS - 1 : S - 1;
     const int c_hi = held + t_last;                         // newest key this block can see
-    int j_start = window > 0 ? held + t0 - window + 1 : 0;
-    if (j_start < first_real) j_start = first_real;
-    if (j_start < 0) j_start = 0;
+    const int j_start = visible_from(held + t0, first_real, window, chunk);
     const int r0 = t0 + wid * 16;                           // this warp's rows
     const int tr[2] = {r0 + gr, r0 + gr + 8};
     int row_c[2], row_lo[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         row_c[i] = held + tr[i];
-        int lo = window > 0 ? row_c[i] - window + 1 : 0;
-        if (lo < first_real) lo = first_real;
-        if (lo < 0) lo = 0;
-        row_lo[i] = lo;
+        row_lo[i] = visible_from(row_c[i], first_real, window, chunk);
         if (tr[i] >= S || row_c[i] < first_real) { row_c[i] = -1; row_lo[i] = 0; }      // nothing visible
     }
     const int warp_hi = held + ((r0 + 15 < S - 1) ? r0 + 15 : S - 1);
-    const int warp_lo = window > 0 ? held + r0 - window + 1 : 0;
+    const int warp_lo = visible_from(held + r0, first_real, window, chunk);
     uint32_t qa[KDMAX][4];
 #pragma unroll
     for (int kd = 0; kd < KDMAX; ++kd) {
@@ -479,7 +535,7 @@ constexpr int SH_KEYS = 64, SH_SSTRIDE = 72, SH_MIN_CHUNK = 64, SH_MAX_SPLITS = 
 template <typename T, int NT, bool SAME>                   // vdim = 64 NT (each warp owns 8 NT value columns)
 __global__ void __launch_bounds__(256) shared_head_attention_kernel(
         const T* __restrict__ q, long q_ld, long q_hs, const T* __restrict__ k, long k_bs, long k_ps, long k_hs, const T* __restrict__ v, long v_bs, long v_ps,
-        long v_hs, int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* __restrict__ pad, int window, float scale,
+        long v_hs, int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* __restrict__ pad, int window, int chunk, float scale,
         float softcap, float* __restrict__ ws, int splits, int tiles, const int32_t* __restrict__ dyn) {
     constexpr int vdim = 64 * NT;
     extern __shared__ __align__(16) unsigned char sh_raw[];
@@ -501,9 +557,7 @@ __global__ void __launch_bounds__(256) shared_head_attention_kernel(
         int c = -1, lo = 0;
         if (r < n_rows) {
             c = held + r / gs;
-            lo = window > 0 ? c - window + 1 : 0;
-            if (lo < first_real) lo = first_real;
-            if (lo < 0) lo = 0;
+            lo = visible_from(c, first_real, window, chunk);
             if (c < first_real) c = -1;
         }
         row_c[tid] = c;
@@ -735,7 +789,7 @@ static size_t shared_head_smem(int dim, int vdim, bool same) {
 
 template <typename T, int NT>
 static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs,
-                              int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* pad, int window, float scale,
+                              int B, int S, int heads, int kv_heads, int dim, int held, int shift, const int32_t* pad, int window, int chunk, float scale,
                               float softcap, const void* sink, void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
     const int vdim = 64 * NT;
     const int tiles = (S * (heads / kv_heads) + 15) / 16, splits = shared_head_splits(B, S, heads, kv_heads);
@@ -747,12 +801,12 @@ static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k
         auto fn = shared_head_attention_kernel<T, NT, true>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
         fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
-                                        shift, pad, window, scale, softcap, ws, splits, tiles, dyn);
+                                        shift, pad, window, chunk, scale, softcap, ws, splits, tiles, dyn);
     } else {
         auto fn = shared_head_attention_kernel<T, NT, false>;
         if ((err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)err;
         fn<<<grid, 256, smem, stream>>>((const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held,
-                                        shift, pad, window, scale, softcap, ws, splits, tiles, dyn);
+                                        shift, pad, window, chunk, scale, softcap, ws, splits, tiles, dyn);
     }
     if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
     shared_head_merge_kernel<T><<<dim3(16 * tiles * kv_heads, B), 256, 0, stream>>>(ws, S, heads, kv_heads, vdim, splits, tiles, (const T*)sink, (T*)out, ld_out, out_col);
@@ -760,9 +814,9 @@ static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k
 }
 
 #define SA_TC_PARAMS const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v, long v_bs, long v_ps, long v_hs, \
-    int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, float scale, float softcap,  \
+    int B, int S, int heads, int kv_heads, int dim, int vdim, int held, int shift, const int32_t* pad, int window, int chunk, float scale, float softcap,  \
     const void* sink, void* out, long ld_out, int out_col, cudaStream_t stream
-#define SA_TC_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, scale, softcap, \
+#define SA_TC_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, chunk, scale, softcap, \
     sink, out, ld_out, out_col, stream
 
 template <typename T, int KDMAX, int NDMAX>
@@ -774,7 +828,7 @@ static int launch_softmax_tc(SA_TC_PARAMS) {
         if (err != cudaSuccess) return (int)err;
     }
     softmax_attention_tc_kernel<T, KDMAX, NDMAX><<<grid, 128, smem, stream>>>(
-        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, chunk,
         scale, softcap, (const T*)sink, (T*)out, ld_out, out_col);
     return mixers_status();
 }
@@ -816,15 +870,32 @@ extern "C" int mixers_wide_qkv_prepare(int dtype, const void* proj, int B, int S
     return mixers_status();
 }
 
+extern "C" int mixers_rope_qk_prepare(int dtype, const void* proj, int B, int S, int ld, int off_q, int off_k, int off_v, int heads, int kv_heads,
+                                      int q_dim, int k_dim, int vdim, int q_rot_off, int k_rot_off, int rot_dims, const double* inv_freq, float amp,
+                                      const void* k_norm_w, int k_norm_cols, float eps, void* q_out, void* k_store, long k_bs, long k_ps,
+                                      long k_hs, void* v_store, long v_bs, long v_ps, long v_hs, int held, int shift, const int32_t* pad,
+                                      const int32_t* dyn, mixers_stream_t stream) {
+    if (B <= 0 || S <= 0) return 0;
+    if (rot_dims < 0 || (rot_dims & 1) || q_rot_off < 0 || k_rot_off < 0 || q_rot_off + rot_dims > q_dim || k_rot_off + rot_dims > k_dim ||
+        kv_heads < 1 || heads < 1 || (rot_dims > 0 && !inv_freq) || (k_norm_w && (k_norm_cols < 1 || k_norm_cols > k_rot_off)) || (vdim > 0 && !v_store))
+        return (int)cudaErrorInvalidValue;
+    const long warps = (long)B * S * (heads + kv_heads + (vdim > 0 ? kv_heads : 0));
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    MIXERS_DISPATCH(dtype, rope_qk_prepare_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        (const T*)proj, B, S, ld, off_q, off_k, off_v, heads, kv_heads, q_dim, k_dim, vdim, q_rot_off, k_rot_off, rot_dims, inv_freq, amp,
+        (const T*)k_norm_w, k_norm_cols, eps, (T*)q_out, (T*)k_store, k_bs, k_ps, k_hs, (T*)v_store, v_bs, v_ps, v_hs, held, shift, pad, dyn));
+    return mixers_status();
+}
+
 extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, long q_hs, const void* k, long k_bs, long k_ps, long k_hs, const void* v,
                                         long v_bs, long v_ps, long v_hs, int B, int S, int heads, int kv_heads, int dim, int vdim, int held,
-                                        int shift, const int32_t* pad, int window, float scale, float softcap, const void* sink, void* out,
+                                        int shift, const int32_t* pad, int window, int chunk, float scale, float softcap, const void* sink, void* out,
                                         long ld_out, int out_col, const int32_t* dyn, int allow_tensor_cores, float* ws, mixers_stream_t stream_) {
     if (B <= 0 || S <= 0) return 0;
     cudaStream_t stream = (cudaStream_t)stream_;
     const int dim4 = (dim + 3) & ~3;
     size_t smem = ((size_t)dim4 + 2 * SA_WARPS + SA_WARPS * SA_VCOLS * 32) * sizeof(float);
-    if (window < 0 || kv_heads < 1 || heads % kv_heads != 0 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (window < 0 || chunk < 0 || kv_heads < 1 || heads % kv_heads != 0 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     const size_t esz = dtype == 0 ? 4 : 2;
     auto mult8 = [](long s) { return (s & 7) == 0; };
     const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
@@ -832,7 +903,7 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, lon
     const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
     if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && (q_hs & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
         (ld_out & 1) == 0 && (out_col & 1) == 0 && shared_head_smem(dim, vdim, same_kv) <= 227 * 1024) {
-#define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, scale, softcap, sink, out, ld_out, out_col, dyn, ws, stream
+#define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, chunk, scale, softcap, sink, out, ld_out, out_col, dyn, ws, stream
         if (dtype == 1) return vdim == 128 ? launch_shared_head<__nv_bfloat16, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__nv_bfloat16, 4>(SH_ARGS)
                                                                                                        : launch_shared_head<__nv_bfloat16, 8>(SH_ARGS);
         return vdim == 128 ? launch_shared_head<__half, 2>(SH_ARGS) : vdim == 256 ? launch_shared_head<__half, 4>(SH_ARGS)
@@ -846,7 +917,7 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, lon
     }
     long items = (long)B * S * heads;
     MIXERS_DISPATCH(dtype, softmax_attention_kernel<T><<<(unsigned)items, SA_WARPS * 32, smem, stream>>>(
-        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window,
+        (const T*)q, q_ld, q_hs, (const T*)k, k_bs, k_ps, k_hs, (const T*)v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, vdim, held, shift, pad, window, chunk,
         scale, softcap, (const T*)sink, (T*)out, ld_out, out_col, dyn, rows16 ? 1 : 0));
     return mixers_status();
 }

@@ -32,7 +32,20 @@ _SIGNATURES = {
                                                                  _c_ptr, _c_ptr],
     "mixers_gated_linear_attention": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_gated_rms_norm": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_int,
-                              _c_float, _c_ptr],
+                              _c_float, _c_int, _c_ptr],
+    "mixers_short_conv": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_channel_delta_rule": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                                                                   _c_ptr, _c_ptr],
+    "mixers_state_space_scan": [_c_int, _c_ptr] + [_c_int] * 6 + [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                                                                 _c_ptr, _c_ptr],
+    "mixers_sigmoid_gate": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+    "mixers_rms_pair_sum": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_float, _c_long, _c_int, _c_ptr, _c_ptr],
+    "mixers_sum_residual_norms": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_long, _c_int,
+                                  _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_gelu_erf": [_c_int, _c_ptr, _c_long, _c_ptr, _c_ptr],
+    "mixers_rope_qk_prepare": [_c_int, _c_ptr] + [_c_int] * 14 + [_c_ptr, _c_float, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr, _c_long, _c_long,
+                                                                 _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "mixers_moe_scatter_scaled": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "mixers_token_shift_mix": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_wkv": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
                    _c_ptr],
@@ -55,10 +68,10 @@ _SIGNATURES = {
     "mixers_latent_prepare": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_float, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_softmax_attention": [_c_int, _c_ptr, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long, _c_ptr, _c_long, _c_long, _c_long] + [_c_int] * 8
-                                + [_c_ptr, _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
+                                + [_c_ptr, _c_int, _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_long, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "mixers_grouped_router": [_c_int, _c_ptr, _c_long, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_small": [_c_int, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
-                         _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+                         _c_int, _c_int, _c_float, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_sort": [_c_ptr, _c_long, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "mixers_moe_combine": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_long, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
 }

@@ -175,6 +175,10 @@ def _optimize_pre(model, qtype=None):
         import functools
         from ipex_llm_b200.transformers.models.zubedra import merge_projections
         model.apply(functools.partial(merge_projections, stack=qtype is None))
+    elif model_type == "nikedra":
+        # everything that reads a mixer's input (a parallel mixer: both branches' projections) -> one in_proj
+        from ipex_llm_b200.transformers.models.nikedra import merge_projections
+        model.apply(merge_projections)
     return model
 
 
@@ -206,7 +210,7 @@ def _optimize_post(model):
         convert_forward(model, module.MixtralRMSNorm, rms_norm_forward)
         convert_forward(model, module.MixtralModel, mixtral_model_forward)
         convert_forward(model, module.MixtralAttention, mixtral_attention_forward)
-    elif model_type in ("zafepel", "serotar", "zubedra"):
+    elif model_type in ("zafepel", "serotar", "zubedra", "nikedra"):
         # this package's own model class: its forwards already call the fused operators and pick the state cache;
         # the recorded decode step for such a cache goes behind generate()
         from ipex_llm_b200.transformers.state_decode_graph import install_state_generate

@@ -472,26 +472,34 @@ class RecurrentStateLayer:
     """What a linear recurrence carries from token to token: the matrix state [B, H, D, Dv] in 32-bit floats and, where a
     short convolution precedes it, the last ``taps - 1`` inputs of every channel [B, taps - 1, C].  Over several new tokens the
     convolution kernel reads ``tail`` and writes ``tail_next`` (no thread reads what another has replaced) and the caller copies
-    it back; ``tail`` itself never moves."""
+    it back; ``tail`` itself never moves.  A layer with more than one convolution (one on the mixer's input, another inside the
+    mixer) keeps the further tails under a ``key`` each."""
 
     def __init__(self):
         self.state = None
         self.tail = None
         self.tail_next = None
+        self.more_tails = {}              # key -> [tail, tail_next]
 
     def matrix(self, batch, heads, dim, vdim, device):
         if self.state is None:
             self.state = torch.zeros(batch, heads, dim, vdim, dtype=torch.float32, device=device)
         return self.state
 
-    def tails(self, batch, taps, channels, dtype, device):
+    def tails(self, batch, taps, channels, dtype, device, key=None):
+        if key is not None:
+            pair = self.more_tails.get(key)
+            if pair is None:
+                tail = torch.zeros(batch, max(taps - 1, 1), channels, dtype=dtype, device=device)
+                pair = self.more_tails[key] = [tail, torch.empty_like(tail)]
+            return pair[0], pair[1]
         if self.tail is None:
             self.tail = torch.zeros(batch, max(taps - 1, 1), channels, dtype=dtype, device=device)
             self.tail_next = torch.empty_like(self.tail)
         return self.tail, self.tail_next
 
     def clear(self):
-        for t in (self.state, self.tail, self.tail_next):
+        for t in [self.state, self.tail, self.tail_next] + [t for pair in self.more_tails.values() for t in pair]:
             if t is not None:
                 t.zero_()
 
@@ -500,6 +508,8 @@ class RecurrentStateLayer:
             t = getattr(self, name)
             if t is not None:
                 setattr(self, name, t.index_select(0, index).contiguous())
+        for pair in self.more_tails.values():
+            pair[0], pair[1] = pair[0].index_select(0, index).contiguous(), pair[1].index_select(0, index).contiguous()
 
 
 class MixerStateLayer:

@@ -38,7 +38,8 @@ def save_low_bit(self, save_dir, *args, **kwargs):
 # (``load_pretrained(model_dir, torch_dtype)`` builds it from config.json + model.safetensors)
 NATIVE_ARCHITECTURES = {"Zafepel": "ipex_llm_b200.transformers.models.zafepel",
                         "Serotar": "ipex_llm_b200.transformers.models.serotar",
-                        "Zubedra": "ipex_llm_b200.transformers.models.zubedra"}
+                        "Zubedra": "ipex_llm_b200.transformers.models.zubedra",
+                        "Nikedra": "ipex_llm_b200.transformers.models.nikedra"}
 
 
 def native_architecture(model_dir):

@@ -84,6 +84,53 @@ def short_conv_silu(proj, off, channels, weight, tail, tail_next, slot0, pad):
     return y
 
 
+def short_conv(proj, off, channels, weight, bias, tail, tail_next, slot0, pad, silu=True, add_input=False):
+    """short causal convolution of ``channels`` columns of proj from column ``off`` with an optional bias per channel, silu on
+    the result (``silu``) and / or the token's own input added to it (``add_input``); writes the next tail"""
+    B, S, P = proj.shape
+    taps = weight.shape[1]
+    invalidInputError(proj.is_contiguous() and weight.is_contiguous() and tail.is_contiguous() and tail_next.is_contiguous()
+                      and weight.shape[0] == channels and tail.shape == (B, max(taps - 1, 1), channels)
+                      and (bias is None or (bias.numel() == channels and bias.is_contiguous())), "short_conv: unexpected layout")
+    y = torch.empty(B, S, channels, dtype=proj.dtype, device=proj.device)
+    native.call("mixers_short_conv", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, off, channels, taps, native.ptr(weight),
+                native.ptr(bias), int(bool(silu)) | (int(bool(add_input)) << 1), native.ptr(tail), native.ptr(tail_next), int(slot0),
+                native.ptr(pad), native.ptr(y), native.stream(proj.device))
+    return y
+
+
+def channel_delta_rule(conv, kv_heads, heads, dim, vdim, proj, off_b, z, A_log, dt_bias, state, slot0, pad):
+    """the delta rule with a decay per key channel over the new tokens (conv: q | k | v after the short convolutions; beta from
+    column off_b of proj; z [B, S, heads * dim] decay logits, dt_bias [heads * dim], A_log [heads]); state fp32
+    [B, heads, dim, vdim] in place; returns o fp32 [B, S, heads, vdim]"""
+    B, S, C = conv.shape
+    invalidInputError(C == 2 * kv_heads * dim + heads * vdim and conv.is_contiguous() and proj.is_contiguous() and z.is_contiguous()
+                      and z.numel() == B * S * heads * dim and z.dtype == conv.dtype and dt_bias.numel() == heads * dim
+                      and dt_bias.is_contiguous() and A_log.numel() == heads
+                      and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (B, heads, dim, vdim),
+                      "channel_delta_rule: unexpected layout")
+    o = torch.empty(B, S, heads, vdim, dtype=torch.float32, device=conv.device)
+    native.call("mixers_channel_delta_rule", native.dtype_code(conv.dtype), native.ptr(conv), B, S, kv_heads, heads, dim, vdim, native.ptr(proj),
+                proj.shape[-1], off_b, native.ptr(z), native.ptr(A_log), native.ptr(dt_bias), native.ptr(state), int(slot0), native.ptr(pad),
+                native.ptr(o), native.stream(conv.device))
+    return o
+
+
+def state_space_scan(conv, groups, heads, n_state, vdim, proj, off_dt, A_log, dt_bias, skip, state, slot0, pad):
+    """the state-space recurrence over the new tokens (conv: x | B | C after the short convolution; the step-size logits from
+    column off_dt of proj); state fp32 [B, heads, n_state, vdim] in place; returns y fp32 [B, S, heads, vdim]"""
+    B, S, C = conv.shape
+    invalidInputError(C == heads * vdim + 2 * groups * n_state and conv.is_contiguous() and proj.is_contiguous()
+                      and A_log.numel() == heads and dt_bias.numel() == heads and skip.numel() == heads
+                      and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (B, heads, n_state, vdim),
+                      "state_space_scan: unexpected layout")
+    o = torch.empty(B, S, heads, vdim, dtype=torch.float32, device=conv.device)
+    native.call("mixers_state_space_scan", native.dtype_code(conv.dtype), native.ptr(conv), B, S, groups, heads, n_state, vdim, native.ptr(proj),
+                proj.shape[-1], off_dt, native.ptr(A_log), native.ptr(dt_bias), native.ptr(skip), native.ptr(state), int(slot0),
+                native.ptr(pad), native.ptr(o), native.stream(conv.device))
+    return o
+
+
 def gated_delta_rule(conv, kv_heads, heads, dim, vdim, proj, off_b, off_a, A_log, dt_bias, state, slot0, pad):
     """the delta-rule recurrence over the new tokens; state fp32 [B, heads, dim, vdim] in place; returns o fp32 [B, S, heads, vdim]"""
     B, S, C = conv.shape
@@ -109,16 +156,17 @@ def gated_linear_attention(proj, heads, dim, vdim, z, tau, state, slot0, pad):
     return o
 
 
-def gated_rms_norm(o, gate, off_g, weight, eps, out, out_col, out_scale):
+def gated_rms_norm(o, gate, off_g, weight, eps, out, out_col, out_scale, sigmoid=False, gate_first=False):
     """out[:, out_col:...] = out_scale * rms_norm(o per head) * weight * silu(gate columns from off_g); ``weight`` [vdim] serves
-    every head, [heads * vdim] gives each head its own"""
+    every head, [heads * vdim] gives each head its own.  ``sigmoid``: the gate is sigmoid(.) instead of silu(.); ``gate_first``:
+    the gate multiplies before the norm (the root mean square is that of the gated values)"""
     heads, vdim = o.shape[-2], o.shape[-1]
     n = o.numel() // (heads * vdim)
     invalidInputError(o.is_contiguous() and o.dtype == torch.float32 and gate.is_contiguous() and out.is_contiguous() and out.shape[0] == n
                       and gate.dtype == out.dtype and weight.numel() in (vdim, heads * vdim), "gated_rms_norm: unexpected layout")
     native.call("mixers_gated_rms_norm", native.dtype_code(out.dtype), native.ptr(o), n, heads, vdim, native.ptr(gate), gate.shape[-1], off_g,
                 native.ptr(weight), vdim if weight.numel() == heads * vdim and heads > 1 else 0, float(eps), native.ptr(out), out.shape[1], out_col,
-                float(out_scale), native.stream(out.device))
+                float(out_scale), int(bool(sigmoid)) | (int(bool(gate_first)) << 1), native.stream(out.device))
 
 
 def token_shift_mix(h, mu, tail, tail_next, slot0, pad):
@@ -175,6 +223,80 @@ def wide_qkv_prepare(proj, off_q, off_k, off_v, heads, kv_heads, dim, vdim, q_w,
                 native.ptr(q_w), native.ptr(k_w), float(eps), native.ptr(v_other), v_other.stride(0) if v_other is not None else 0,
                 native.ptr(blend) if v_other is not None else None, native.ptr(q), native.ptr(k_store), native.ptr(v_store), cap, int(held), int(shift),
                 native.ptr(pad), native.ptr(dyn), native.stream(proj.device))
+    return q
+
+
+def sigmoid_gate(o, gate, off_g, per_gate):
+    """o[n, c] *= sigmoid(gate[n, off_g + c // per_gate]) in place (o [N, C] contiguous, gate [N, P] contiguous)"""
+    invalidInputError(o.is_contiguous() and gate.is_contiguous() and o.dim() == 2 and gate.shape[0] == o.shape[0] and gate.dtype == o.dtype,
+                      "sigmoid_gate: unexpected layout")
+    native.call("mixers_sigmoid_gate", native.dtype_code(o.dtype), native.ptr(o), o.shape[0], o.shape[1], native.ptr(gate), gate.shape[-1],
+                int(off_g), int(per_gate), native.stream(o.device))
+    return o
+
+
+def rms_pair_sum(a, b, w_a, w_b, eps, scale):
+    """fp32 [N, W] = scale * (a / rms(a) * w_a + b / rms(b) * w_b)"""
+    a, b = _c(a), _c(b)
+    invalidInputError(a.shape == b.shape and a.dtype == b.dtype == w_a.dtype == w_b.dtype and w_a.numel() == a.shape[1] == w_b.numel(),
+                      "rms_pair_sum: unexpected layout")
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    native.call("mixers_rms_pair_sum", native.dtype_code(a.dtype), native.ptr(a), native.ptr(b), native.ptr(w_a), native.ptr(w_b), float(eps),
+                float(scale), a.shape[0], a.shape[1], native.ptr(out), native.stream(a.device))
+    return out
+
+
+def sum_residual_norms(x, ys, out_dtype, eps, pre_gain=None, stack=None, index=0, coef=None, gain1=None, gain2=None):
+    """x += sum(ys) in place (x fp32 [N, W]; ``ys``: up to two tensors of the model's dtype and two fp32 ones); ``pre_gain``: x is
+    first divided by its root mean square and multiplied by this scalar; with ``stack`` [streams, N, W] the new x is kept as
+    stream ``index`` and, with ``coef`` [index + 1], replaced by the coefficient-weighted sum of streams 0..index.  Returns
+    (x / rms(x) * gain1, x / rms(x) * gain2) in ``out_dtype`` (None where no gain is given)."""
+    n, w = x.shape
+    invalidInputError(x.dtype == torch.float32 and x.is_contiguous(), "sum_residual_norms: x is a contiguous fp32 [N, W]")
+    ys = [y for y in ys if y is not None]
+    if out_dtype == torch.float32:                           # a 32-bit model: every addend fits either pair of slots
+        floats, typed = ys[:2], ys[2:]
+    else:
+        typed, floats = [y for y in ys if y.dtype == out_dtype], [y for y in ys if y.dtype == torch.float32]
+    invalidInputError(len(typed) <= 2 and len(floats) <= 2 and len(typed) + len(floats) == len(ys)
+                      and all(y.shape == x.shape and y.is_contiguous() for y in typed + floats),
+                      "sum_residual_norms: addends are contiguous [N, W] tensors of the model's dtype or fp32")
+    invalidInputError(stack is None or (stack.dtype == torch.float32 and stack.is_contiguous() and stack.shape[1:] == x.shape and index < stack.shape[0]),
+                      "sum_residual_norms: the kept streams are a contiguous fp32 [streams, N, W]")
+    invalidInputError(coef is None or (stack is not None and coef.numel() == index + 1), "sum_residual_norms: one coefficient per kept stream")
+    typed, floats = typed + [None, None], floats + [None, None]
+    h1 = torch.empty(n, w, dtype=out_dtype, device=x.device) if gain1 is not None else None
+    h2 = torch.empty(n, w, dtype=out_dtype, device=x.device) if gain2 is not None else None
+    native.call("mixers_sum_residual_norms", native.dtype_code(out_dtype), native.ptr(x), n, w, native.ptr(typed[0]), native.ptr(typed[1]),
+                native.ptr(floats[0]), native.ptr(floats[1]), native.ptr(pre_gain), float(eps), native.ptr(stack), n * w, int(index),
+                native.ptr(coef), native.ptr(gain1), native.ptr(gain2), native.ptr(h1), native.ptr(h2), native.stream(x.device))
+    return h1, h2
+
+
+def gelu_erf(z):
+    z = _c(z)
+    out = torch.empty_like(z)
+    if z.numel():
+        native.call("mixers_gelu_erf", native.dtype_code(z.dtype), native.ptr(z), z.numel(), native.ptr(out), native.stream(z.device))
+    return out
+
+
+def rope_qk_prepare(proj, off_q, off_k, off_v, heads, kv_heads, q_dim, k_dim, vdim, q_rot_off, k_rot_off, rot_dims, inv_freq, amp, k_store,
+                    k_strides, v_store, v_strides, held, shift, pad, eps=0.0, k_norm_w=None, k_norm_cols=0, dyn=None):
+    """rotary positions on the new tokens' queries and keys (columns of proj [B, S, P]) and the cache write of keys and values;
+    ``k_strides`` / ``v_strides``: (batch, position, head) strides of the caches in elements; ``inv_freq`` float64 [rot_dims / 2],
+    ``amp`` multiplies cosine and sine; ``k_norm_w``: the first ``k_norm_cols`` channels of every key head are RMS-normalised with
+    this weight.  Returns q [B * S, heads * q_dim]"""
+    B, S, P = proj.shape
+    invalidInputError(proj.is_contiguous() and k_store.dtype == proj.dtype and (v_store is None or v_store.dtype == proj.dtype)
+                      and (rot_dims == 0 or (inv_freq.dtype == torch.float64 and inv_freq.numel() == rot_dims // 2 and inv_freq.is_contiguous())),
+                      "rope_qk_prepare: unexpected layout")
+    q = torch.empty(B * S, heads * q_dim, dtype=proj.dtype, device=proj.device)
+    vs = v_strides if v_store is not None else (0, 0, 0)
+    native.call("mixers_rope_qk_prepare", native.dtype_code(proj.dtype), native.ptr(proj), B, S, P, int(off_q), int(off_k), int(off_v), heads, kv_heads,
+                q_dim, k_dim, vdim if v_store is not None else 0, int(q_rot_off), int(k_rot_off), int(rot_dims), native.ptr(inv_freq) if rot_dims else None,
+                float(amp), native.ptr(k_norm_w), int(k_norm_cols), float(eps), native.ptr(q), native.ptr(k_store), *[int(v) for v in k_strides],
+                native.ptr(v_store), *[int(v) for v in vs], int(held), int(shift), native.ptr(pad), native.ptr(dyn), native.stream(proj.device))
     return q
 
 
@@ -276,10 +398,11 @@ def latent_prepare(proj, off_q, q_rank, q_w, off_c, kv_rank, c_w, eps, store, he
 
 
 def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out=None, out_col=0, dyn=None, tensor_cores=True, softcap=0.0,
-                      sink=None):
+                      sink=None, chunk=0):
     """q [B * S, heads * dim], or [B * S, heads, dim] with any token and head strides; k [B, L, kv_heads, dim], v [B, L, kv_heads,
     vdim] views (any strides with a unit last one); returns out [B * S, heads * vdim] in q's dtype.  ``softcap`` > 0 caps the
-    scaled scores (cap * tanh(score / cap)); ``sink`` [heads]: a per-head term exp(sink) in the softmax's denominator"""
+    scaled scores (cap * tanh(score / cap)); ``sink`` [heads]: a per-head term exp(sink) in the softmax's denominator;
+    ``chunk`` > 0: a query sees only the earlier positions of its own chunk of that many positions"""
     kv_heads, dim, vdim = k.shape[2], k.shape[3], v.shape[3]
     q_hs = q.stride(1) if q.dim() == 3 else dim
     invalidInputError(q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.numel() == B * S * heads * dim and k.dtype == q.dtype
@@ -292,7 +415,7 @@ def softmax_attention(q, k, v, B, S, heads, held, shift, pad, window, scale, out
     ws = torch.empty(need, dtype=torch.float32, device=q.device) if need else None
     native.call("mixers_softmax_attention", native.dtype_code(q.dtype), native.ptr(q), q.stride(0), q_hs, native.ptr(k), k.stride(0), k.stride(1),
                 k.stride(2), native.ptr(v), v.stride(0), v.stride(1), v.stride(2), B, S, heads, kv_heads, dim, vdim, int(held), int(shift),
-                native.ptr(pad), int(window), float(scale), float(softcap or 0.0), native.ptr(sink), native.ptr(out), out.stride(0), int(out_col),
+                native.ptr(pad), int(window), int(chunk), float(scale), float(softcap or 0.0), native.ptr(sink), native.ptr(out), out.stride(0), int(out_col),
                 native.ptr(dyn), int(bool(tensor_cores)),
                 native.ptr(ws), native.stream(q.device))
     return out
@@ -317,8 +440,8 @@ def scored_router(h, router, correction, groups, keep, top, sigmoid=True, group_
     their sum if ``renorm``, times ``scale``; ``gate_row`` [1, W]: gate = sigmoid(gate_row . h) for an expert every token runs"""
     h = _c(h)
     n, w = h.shape
-    invalidInputError(router.is_contiguous() and router.shape[1] == w and router.dtype == h.dtype and correction.dtype == h.dtype
-                      and correction.numel() == router.shape[0] and (gate_row is None or (gate_row.numel() == w and gate_row.dtype == h.dtype
+    invalidInputError(router.is_contiguous() and router.shape[1] == w and router.dtype == h.dtype
+                      and (correction is None or (correction.dtype == h.dtype and correction.numel() == router.shape[0])) and (gate_row is None or (gate_row.numel() == w and gate_row.dtype == h.dtype
                                                                                            and gate_row.is_contiguous())),
                       "scored_router: unexpected layout")
     idx = torch.empty(n, top, dtype=torch.int32, device=h.device)
@@ -342,11 +465,12 @@ def clamped_glu(gate_up, cols, limit):
 
 
 def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shared_out, ffs=None, always_on=False, always_w=None, clamped=False,
-              limit=0.0, limit_always=0.0):
+              limit=0.0, limit_always=0.0, ungated_gelu=False, weight_input=False):
     """fp32 [N, W]: the chosen experts of a few tokens through tables of the experts' weight addresses.  ``ffs``: int32 sizes per
     table entry (``ff`` = the largest); ``always_on``: table entry ``n_experts`` is an expert every token runs, with weight
     ``always_w`` [N] (None: 1); ``clamped``: the experts' activation is the clamped form with ``limit`` (``limit_always`` for the
-    always-on expert) instead of silu(g) u"""
+    always-on expert) instead of silu(g) u; ``ungated_gelu``: the experts have no gate, their first matrix is [ff, width] and
+    the activation the exact gelu; ``weight_input``: a chosen expert's weight multiplies its input instead of its output"""
     h = _c(h)
     n, w = h.shape
     top = idx.shape[1]
@@ -354,7 +478,7 @@ def moe_small(h, idx, wgt, gate_up_table, down_table, ff, n_experts, n_out, shar
     y = torch.empty(n, w, dtype=torch.float32, device=h.device)
     native.call("mixers_moe_small", native.dtype_code(h.dtype), native.ptr(h), n, w, int(ff), top, int(n_experts), int(n_out), native.ptr(idx),
                 native.ptr(wgt), native.ptr(gate_up_table), native.ptr(down_table), native.ptr(ffs), int(bool(always_on)), native.ptr(always_w),
-                int(bool(clamped)), float(limit), float(limit_always), native.ptr(shared_out), native.ptr(act), native.ptr(y), native.stream(h.device))
+                2 if ungated_gelu else int(bool(clamped)), int(bool(weight_input)), float(limit), float(limit_always), native.ptr(shared_out), native.ptr(act), native.ptr(y), native.stream(h.device))
     return y
 
 
@@ -370,9 +494,19 @@ def moe_sort(idx, n_keys):
     return counts, pos, token_of
 
 
+def moe_scatter_scaled(h, pos, idx, wgt, n_experts, n_rows):
+    """[n_rows, W] in h's dtype: row pos[n, k] = h[n] * wgt[n, k] for every choice of an expert (the experts' sorted, weighted inputs)"""
+    h = _c(h)
+    n, top = idx.shape
+    rows = torch.empty(max(n_rows, 1), h.shape[1], dtype=h.dtype, device=h.device)
+    native.call("mixers_moe_scatter_scaled", native.dtype_code(h.dtype), native.ptr(h), native.ptr(pos), native.ptr(idx), native.ptr(wgt), n * top, top,
+                h.shape[1], int(n_experts), native.ptr(rows), native.stream(h.device))
+    return rows
+
+
 def moe_combine(rows, pos, idx, wgt, h, shared_out, n_experts, n_out, shared_w=None):
     """fp32 [N, W]: weighted sum of the experts' outputs ``rows`` (row pos[n, k] belongs to token n's k-th choice) + shared_out
-    (times ``shared_w`` [N] when given)"""
+    (times ``shared_w`` [N] when given); ``wgt`` None: every weight is 1"""
     h = _c(h)
     n, w = h.shape
     y = torch.empty(n, w, dtype=torch.float32, device=h.device)
