@@ -270,6 +270,8 @@ def lowbit_matmul(x_2d: torch.Tensor, weight: torch.Tensor, weight_shape, qtype:
         invalidInputError(False, f"activation last dim {x_2d.shape[1]} != in_features {K}")
     if not x_2d.is_contiguous():
         x_2d = x_2d.contiguous()
+    elif x_2d.data_ptr() % 16:
+        x_2d = x_2d.clone()                                  # one row cut out of a wider one: contiguous, but the kernels load 16 bytes at a time
     out_dtype = out_dtype or (out.dtype if out is not None else x_2d.dtype)
     if out is None:
         invalidInputError(not accumulate, "accumulate needs an output tensor")

@@ -244,7 +244,7 @@ MIXERS = {"latent_attention": latent_attention_mixer, "channel_delta": channel_d
 
 
 def forward(cfg, weights, tokens, collect=None, margins=None):
-    """logits [T, vocab] of one sequence; ``collect``: a list that receives the stream after every layer (before the depth
+    """logits [T, vocab] of one sequence; ``collect``: a list that receives what every layer hands on (behind the depth
     average); ``margins``: a list that receives every routed layer's route_margins"""
     eps = float(cfg["norm"]["eps"])
     taps = int(cfg["canon"]["taps"])
@@ -266,9 +266,146 @@ def forward(cfg, weights, tokens, collect=None, margins=None):
                     margins.append(route_margins(h2, W["mlp.router"], int(mlp["router"]["top"])))
                 y = y + input_weighted_experts(h2, sub(W, "mlp."), mlp)
         x = x + y
-        if collect is not None:
-            collect.append(x.clone())
         streams.append(x)
         x = sum(W["dwa"][j] * streams[j] for j in range(i + 2))
+        if collect is not None:
+            collect.append(x.clone())
     x = unit_rms(x, eps) * weights["final.norm"]
     return (x @ weights["head"].T) * float(cfg["logit_scale"])
+
+
+def greedy(cfg, weights, prompt, n_new):
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(forward(cfg, weights, tokens)[-1].argmax()))
+    return tokens
+
+
+# ------------------------------------------------------------------ pieces the kernel tests address directly
+def visible_attention(q, k, v, scale, held=0, first=0, window=0, chunk=0, origin=None):
+    """q [S, H, D]: new tokens that sit at indices held .. held + S - 1 of k [L, G, D] / v [L, G, Dv]; indices below ``first`` do
+    not exist (padding); ``origin``: the index that holds position 0 (``first`` unless earlier positions have left the storage,
+    then negative).  ``window`` > 0: a query sees itself and the window - 1 positions before it; ``chunk`` > 0: only the earlier
+    positions of its own chunk of positions.  Returns [S, H, Dv] (zeros where no query exists)."""
+    S, H, D = q.shape
+    per = H // k.shape[1]
+    origin = first if origin is None else origin
+    out = torch.zeros(S, H, v.shape[2], dtype=q.dtype)
+    for t in range(S):
+        c = held + t
+        if c < first:
+            continue
+        lo = first
+        if window:
+            lo = max(lo, c - window + 1)
+        if chunk:
+            lo = max(lo, origin + ((c - origin) // chunk) * chunk)
+        for hd in range(H):
+            s = (k[lo:c + 1, hd // per] @ q[t, hd]) * scale
+            out[t, hd] = torch.softmax(s, dim=0) @ v[lo:c + 1, hd // per]
+    return out
+
+
+# ------------------------------------------------------------------ random models
+LATENT = dict(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=12, window=9, base=100.0, scale=0.3)
+DELTA = dict(heads=4, kv_heads=2, dim=12, vdim=10, conv=4)
+LEFT = dict(heads=6, kv_heads=2, dim=12, vdim=10, rot_dims=8, base=50.0, chunk=7, scale=0.25, factor=4.0, original=16, fast=4.0, slow=1.0)
+RIGHT = dict(heads=4, vdim=6, state=10, groups=2, norm_groups=2, conv=2)
+DENSE = dict(ff=24, limit=0.7)
+MOE = dict(experts=5, top=2, ff=12)
+
+
+def random_config(width=40, vocab=61, taps=3, order=("latent_attention", "channel_delta", "parallel", "channel_delta"),
+                  mlps=("dense", "moe", None, "moe"), latent=None, delta=None, left=None, right=None, dense=None, moe=None, eps=1e-5,
+                  logit_scale=0.5):
+    """``order``: the layers' mixers; ``mlps``: per layer "dense", "moe" or None; the dicts override the sizes above"""
+    la, de, le, ri, dn, mo = (dict(base, **(over or {})) for base, over in ((LATENT, latent), (DELTA, delta), (LEFT, left), (RIGHT, right),
+                                                                             (DENSE, dense), (MOE, moe)))
+    layers = []
+    for kind, ff in zip(order, mlps):
+        if kind == "latent_attention":
+            mixer = {"heads": la["heads"], "dim": la["dim"], "rot_dim": la["rot_dim"], "vdim": la["vdim"], "kv_rank": la["kv_rank"],
+                     "scale": la["scale"], "mask": {"size": la["window"]}, "rot": {"base": la["base"], "dims": la["rot_dim"]}}
+        elif kind == "channel_delta":
+            mixer = {k: de[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv")}
+        else:
+            rot = {"base": le["base"], "dims": le["rot_dims"]}
+            if le["factor"]:
+                rot["scaling"] = {k: le[k] for k in ("factor", "original", "fast", "slow")}
+            mixer = {"left": {"heads": le["heads"], "kv_heads": le["kv_heads"], "dim": le["dim"], "vdim": le["vdim"], "scale": le["scale"],
+                              "mask": {"size": le["chunk"]}, "rot": rot},
+                     "right": {k: ri[k] for k in ("heads", "vdim", "state", "groups", "norm_groups", "conv")}}
+        mlp = None
+        if ff == "dense":
+            mlp = {"kind": "dense", "ff": dn["ff"], "limit": dn["limit"]}
+        elif ff == "moe":
+            mlp = {"kind": "moe", "expert": {"ff": mo["ff"]}, "router": {"experts": mo["experts"], "top": mo["top"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Nikedra", "vocab": vocab, "width": width, "canon": {"taps": taps}, "norm": {"eps": eps}, "layers": layers,
+            "logit_scale": logit_scale}
+
+
+def random_weights(cfg, seed, ranks=(5, 3), dtype=torch.bfloat16):
+    """weights under the checkpoint's names; ``ranks``: the inner sizes of a channel_delta layer's decay and gate projections"""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+    taps = cfg["canon"]["taps"]
+
+    def mat(o, i, s=1.0):
+        return torch.randn(o, i, generator=g) * (s / math.sqrt(i))
+
+    def vec(n, mean=1.0, s=0.2):
+        return mean + torch.randn(n, generator=g) * s
+
+    def gain():
+        return torch.rand((), generator=g) * 1.0 + 0.6
+
+    w = {"embed": torch.randn(cfg["vocab"], W, generator=g), "embed.norm": gain(), "final.norm": gain(), "head": mat(cfg["vocab"], W)}
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        w[p + "norm1"] = gain()
+        w[p + "canon1"] = torch.randn(W, taps, generator=g) * 0.4
+        dwa = torch.randn(i + 2, generator=g) * 0.3
+        dwa[-1] += 1.0                                                      # mostly the layer's own result, some of every earlier stream
+        w[p + "dwa"] = dwa
+        x = p + "mix."
+        if lc["type"] == "latent_attention":
+            H, D, Dr, Dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            w[x + "q"], w[x + "dkv"], w[x + "g"] = mat(H * (D + Dr), W, 2.0), mat(R + Dr, W, 2.0), mat(H * Dv, W)
+            w[x + "dkv.norm"] = vec(R, 1.0, 0.4)
+            w[x + "uk"], w[x + "uv"], w[x + "o"] = mat(H * D, R, 2.0), mat(H * Dv, R), mat(W, H * Dv)
+        elif lc["type"] == "channel_delta":
+            H, G, D, Dv, T = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            w[x + "q"], w[x + "k"], w[x + "v"], w[x + "b"] = mat(G * D, W, 2.0), mat(G * D, W, 2.0), mat(H * Dv, W, 2.0), mat(H, W, 2.0)
+            for n, c in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                w[x + n + ".conv"] = torch.randn(c, T, generator=g) * 0.6
+            w[x + "a1"], w[x + "a2"] = mat(ranks[0], W), mat(H * D, ranks[0], 2.0)
+            w[x + "g1"], w[x + "g2"] = mat(ranks[1], W), mat(H * Dv, ranks[1], 2.0)
+            w[x + "A_log"], w[x + "dt_bias"] = torch.randn(H, generator=g) * 0.7 - 0.5, torch.randn(H * D, generator=g) - 1.0
+            w[x + "norm"], w[x + "o"] = vec(Dv), mat(W, H * Dv)
+        else:
+            l, r = m["left"], m["right"]
+            H, G, D, Dv = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+            w[x + "left.q"], w[x + "left.k"], w[x + "left.v"] = mat(H * D, W, 2.0), mat(G * D, W, 2.0), mat(G * Dv, W)
+            w[x + "left.g"], w[x + "left.o"], w[x + "left.out"] = mat(H, W, 2.0), mat(W, H * Dv), vec(W)
+            Hs, P, N, Gs, T = r["heads"], r["vdim"], r["state"], r["groups"], r["conv"]
+            inner, C = Hs * P, Hs * P + 2 * Gs * N
+            w[x + "right.in"] = mat(2 * inner + 2 * Gs * N + Hs, W, 1.5)
+            w[x + "right.conv"], w[x + "right.conv.b"] = torch.randn(C, T, generator=g) * 0.6, torch.randn(C, generator=g) * 0.3
+            w[x + "right.dt_bias"], w[x + "right.A_log"] = torch.randn(Hs, generator=g) - 0.5, torch.randn(Hs, generator=g) * 0.7 - 0.5
+            w[x + "right.D"], w[x + "right.norm"] = vec(Hs, 0.5, 0.5), vec(inner)
+            w[x + "right.o"], w[x + "right.out"] = mat(W, inner), vec(W)
+        ff = lc.get("mlp")
+        if ff is not None:
+            w[p + "norm2"] = gain()
+            y = p + "mlp."
+            if ff["kind"] == "dense":
+                F = ff["ff"]
+                w[y + "gate"], w[y + "up"], w[y + "down"] = mat(F, W, 2.0), mat(F, W, 2.0), mat(W, F)
+                w[y + "gate.b"], w[y + "up.b"], w[y + "down.b"] = (torch.randn(n, generator=g) * 0.3 for n in (F, F, W))
+            else:
+                E, F = ff["router"]["experts"], ff["expert"]["ff"]
+                for e in range(E):
+                    w[y + f"e{e}.up"], w[y + f"e{e}.down"] = mat(F, W, 2.0), mat(W, F)
+                w[y + "router"] = mat(E, W, 3.0)
+    return {k: v.to(dtype) for k, v in w.items()}
