@@ -687,11 +687,12 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-tp", action="store_true")
     ap.add_argument("--fused-mlp", type=int, default=1, dest="fused_mlp")
-    ap.add_argument("--arch", default="llama", choices=["llama", "zafepel", "serotar", "zubedra"],
-                    help="llama: the headline workload (default, unchanged); zafepel / serotar / zubedra: that design at real layer sizes "
-                         "beside the closest model of equal size (a Llama / a Mixtral / a Serotar), with every kernel of the design against "
-                         "its roofline (bench_mixers.py / bench_serotar.py / bench_zubedra.py)")
-    ap.add_argument("--no-compare", action="store_true", help="--arch zafepel / serotar / zubedra: leave out the model of equal size")
+    ap.add_argument("--arch", default="llama", choices=["llama", "zafepel", "serotar", "zubedra", "nikedra"],
+                    help="llama: the headline workload (default, unchanged); zafepel / serotar / zubedra / nikedra: that design at real layer sizes "
+                         "beside the closest model of equal size (a Llama / a Mixtral / a Serotar / a Serotar), with every kernel of the design "
+                         "against its roofline (bench_mixers.py / bench_serotar.py / bench_zubedra.py / bench_nikedra.py)")
+    ap.add_argument("--no-compare", action="store_true", help="--arch zafepel / serotar / zubedra / nikedra: leave out the model of equal size")
+    ap.add_argument("--sizes", default=None, help="--arch nikedra: only these of its sets of layer sizes (comma-separated, e.g. 2048)")
     args = ap.parse_args()
     if args.arch == "zafepel":
         import bench_mixers
@@ -704,6 +705,10 @@ def main():
     if args.arch == "zubedra":
         import bench_zubedra
         bench_zubedra.run(args)
+        return
+    if args.arch == "nikedra":
+        import bench_nikedra
+        bench_nikedra.run(args)
         return
     global FUSED_MLP
     FUSED_MLP = bool(args.fused_mlp)

@@ -130,6 +130,53 @@ __global__ void gated_rms_norm_kernel(const float* __restrict__ o, long n_rows, 
         dst[c] = from_f<T>(src[c] * inv * to_f(w[c]) * gated(c) * out_scale);
 }
 
+// the same for wide heads (a state-space branch normalises its whole inner width in a few parts): one block per (row, head), the
+// head's values -- gated already when the gate comes first -- stay in registers between the sum of squares and the write
+constexpr int GN_MAXC = 8;
+__device__ __forceinline__ float gn_block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int nw = (blockDim.x + 31) >> 5;
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.0f;
+    for (int i = 0; i < nw; ++i) s += red[i];
+    return s;
+}
+
+template <typename T>
+__global__ void gated_rms_norm_wide_kernel(const float* __restrict__ o, int heads, int vdim, const T* __restrict__ gate, int ld_gate, int off_g,
+                                           const T* __restrict__ w, int w_head_stride, float eps, T* __restrict__ out, int ld_out, int out_col,
+                                           float out_scale, int gate_mode) {
+    __shared__ float red[32];
+    const long item = blockIdx.x;
+    const long n = item / heads;
+    const int h = (int)(item - n * heads);
+    const float* src = o + item * (long)vdim;
+    const T* g = gate + n * (long)ld_gate + off_g + h * vdim;
+    const bool first = (gate_mode & 2) != 0;
+    float v[GN_MAXC], gt[GN_MAXC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < GN_MAXC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = 0.0f; gt[k] = 0.0f;
+        if (c < vdim) {
+            const float z = to_f(g[c]);
+            gt[k] = (gate_mode & 1) ? sigmoid_f(z) : silu_f(z);
+            v[k] = first ? src[c] * gt[k] : src[c];
+            ss += v[k] * v[k];
+        }
+    }
+    const float inv = out_scale / sqrtf(gn_block_sum(ss, red) / (float)vdim + eps);
+    T* dst = out + n * (long)ld_out + out_col + h * vdim;
+    w += (long)h * w_head_stride;
+#pragma unroll
+    for (int k = 0; k < GN_MAXC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < vdim) dst[c] = from_f<T>(v[k] * inv * to_f(w[c]) * (first ? 1.0f : gt[k]));
+    }
+}
+
 // o[n, c] *= sigmoid(gate[n, off_g + c / per_gate]) in place: a gate per channel (per_gate 1) or one per head (per_gate = the
 // head's channels)
 template <typename T>
@@ -242,6 +289,15 @@ extern "C" int mixers_gated_rms_norm(int dtype, const float* o, long n_rows, int
     if (n_rows <= 0) return 0;
     if (gate_mode & ~3) return (int)cudaErrorInvalidValue;
     long warps = n_rows * heads;
+    if (vdim > 256 && vdim <= GN_MAXC * 1024 && warps <= 1024) {   // few wide heads (a decoding step): a block each; many rows keep every SM
+                                                                    // busy with a warp each
+        int threads = 128;
+        while (threads < 1024 && threads * GN_MAXC < vdim) threads <<= 1;
+        if (threads * 4 <= vdim && threads < 1024) threads <<= 1;   // at least two rounds of loads in flight per thread are enough
+        MIXERS_DISPATCH(dtype, gated_rms_norm_wide_kernel<T><<<(unsigned)warps, threads, 0, (cudaStream_t)stream>>>(
+            o, heads, vdim, (const T*)gate, ld_gate, off_g, (const T*)w, w_head_stride, eps, (T*)out, ld_out, out_col, out_scale, gate_mode));
+        return mixers_status();
+    }
     int blocks = (int)((warps + 3) / 4);
     MIXERS_DISPATCH(dtype, gated_rms_norm_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(o, n_rows, heads, vdim, (const T*)gate, ld_gate, off_g,
                                                                                                 (const T*)w, w_head_stride, eps, (T*)out, ld_out, out_col,

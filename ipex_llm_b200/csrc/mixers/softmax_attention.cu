@@ -778,7 +778,7 @@ static int shared_head_splits(int B, int S, int heads, int kv_heads) {
 }
 
 static bool shared_head_ok(int dtype, int S, int heads, int kv_heads, int dim, int vdim) {
-    return dtype != 0 && kv_heads >= 1 && heads % kv_heads == 0 && heads / kv_heads >= 4 && S <= 16 && dim % 16 == 0 && dim <= 512 &&
+    return dtype != 0 && kv_heads >= 1 && heads % kv_heads == 0 && heads / kv_heads >= 4 && S <= 16 && dim % 16 == 0 && dim <= 1024 &&
            (vdim == 128 || vdim == 256 || vdim == 512);
 }
 
@@ -793,7 +793,7 @@ static int launch_shared_head(const void* q, long q_ld, long q_hs, const void* k
                               float softcap, const void* sink, void* out, long ld_out, int out_col, const int32_t* dyn, float* ws, cudaStream_t stream) {
     const int vdim = 64 * NT;
     const int tiles = (S * (heads / kv_heads) + 15) / 16, splits = shared_head_splits(B, S, heads, kv_heads);
-    const bool same = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
+    const bool same = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim >= vdim;     // the values are the keys' first channels
     const size_t smem = shared_head_smem(dim, vdim, same);
     dim3 grid(splits, tiles * kv_heads, B);
     cudaError_t err;
@@ -900,7 +900,7 @@ extern "C" int mixers_softmax_attention(int dtype, const void* q, long q_ld, lon
     auto mult8 = [](long s) { return (s & 7) == 0; };
     const bool rows16 = esz == 2 && mult8(k_bs) && mult8(k_ps) && mult8(k_hs) && mult8(v_bs) && mult8(v_ps) && mult8(v_hs) &&
                         ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && (dim & 7) == 0;
-    const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim == vdim;
+    const bool same_kv = k == v && k_bs == v_bs && k_ps == v_ps && k_hs == v_hs && dim >= vdim;
     if (allow_tensor_cores && ws && rows16 && shared_head_ok(dtype, S, heads, kv_heads, dim, vdim) && (q_ld & 7) == 0 && (q_hs & 7) == 0 && ((uintptr_t)q & 15) == 0 &&
         (ld_out & 1) == 0 && (out_col & 1) == 0 && shared_head_smem(dim, vdim, same_kv) <= 227 * 1024) {
 #define SH_ARGS q, q_ld, q_hs, k, k_bs, k_ps, k_hs, v, v_bs, v_ps, v_hs, B, S, heads, kv_heads, dim, held, shift, pad, window, chunk, scale, softcap, sink, out, ld_out, out_col, dyn, ws, stream

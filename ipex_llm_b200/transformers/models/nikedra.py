@@ -41,6 +41,7 @@ from ipex_llm_b200.transformers.models.utils import read_safetensors
 from ipex_llm_b200.utils.common import invalidInputError
 
 ABSORB_MAX_TOKENS = 16        # up to this many new tokens per row attend to the latent cache itself (no key / value expansion)
+OVERLAP_MIN_TOKENS = 256      # from this many new tokens on, a layer's feed-forward runs on a second stream beside its mixer
 YARN_AMP_SLOPE = 0.1          # cosine and sine of rescaled frequencies are multiplied by slope * ln(factor) + 1
 
 
@@ -316,6 +317,8 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
         self.lm_head = nn.Linear(config.width, config.vocab, bias=False)
         self.collect_residual = None          # a list: gets the residual stream after every layer (debugging aid)
         self.attention_tensor_cores = True    # 16-bit models: prompts take the tensor-core attention kernel
+        self.overlap_feed_forward = True      # prompts: mixer and feed-forward read the same stream, so they run side by side
+        self._side_stream = None
 
     def _init_weights(self, module):
         pass
@@ -327,6 +330,15 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
         return self.lm_head
 
     # ---- helpers
+    def _plain_linears(self):
+        """no projection was converted to a low-bit format (those products share one workspace per device, so two of them
+        must not run on two streams at once)"""
+        plain = self.__dict__.get("_b200_plain_linears")
+        if plain is None:
+            plain = self.__dict__["_b200_plain_linears"] = all(type(m) is nn.Linear for m in self.modules() if isinstance(m, nn.Linear) or
+                                                               type(m).__name__ == "LowBitLinear")
+        return plain
+
     @staticmethod
     def _conv(proj, off, channels, weight, bias, rec, key, B, S, cache, silu, add_input=False):
         """a short causal convolution over the new tokens and the state's tail (which keeps its address: a recorded step holds it)"""
@@ -378,12 +390,13 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
         w = mx.expand.weight
         if S <= ABSORB_MAX_TOKENS:
             # few new tokens: the query of head h moves into the cache rows' space (W_uk_h^T q | rotated q), the cache itself is
-            # key and value of one shared head, and W_uv_h maps the weighted rows back
-            wk, wv = w[:H * Dq].view(H, Dq, Rk), w[H * Dq:].view(H, Dv, Rk)
+            # the key of one shared head, its latent part (the first R numbers of a row) the value, and W_uv_h maps the weighted
+            # latents back
+            wk, wv = w[:H * Dq].view(H, Dq, Rk), w[H * Dq:].view(H, Dv, Rk)[:, :, :R]
             qa = torch.matmul(q.view(N, H, Dq).transpose(0, 1), wk).transpose(0, 1)                  # [N, H, Rk], stored head by head
             rows = store.unsqueeze(2)                                        # [B, capacity, 1, Rk]
-            o_rows = ops.softmax_attention(qa, rows, rows, B, S, H, held, shift, cache.pad, mx.window, mx.scale, dyn=dyn)
-            o = torch.matmul(o_rows.view(N, H, Rk).transpose(0, 1), wv.transpose(1, 2)).transpose(0, 1).reshape(N, H * Dv)
+            o_rows = ops.softmax_attention(qa, rows, rows[..., :R], B, S, H, held, shift, cache.pad, mx.window, mx.scale, dyn=dyn)
+            o = torch.matmul(o_rows.view(N, H, R).transpose(0, 1), wv.transpose(1, 2)).transpose(0, 1).reshape(N, H * Dv)
         else:
             # a prompt or a long portion: keys and values of the positions that some new token still sees, expanded from the cache
             first = max(held - (mx.window - 1), 0)
@@ -481,6 +494,13 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
             layer = core.layers[i]
             return layer.norm1.weight, (layer.norm2.weight if layer.mlp is not None else None)
 
+        main = side = forked = None
+        if (self.overlap_feed_forward and B * S >= OVERLAP_MIN_TOKENS and dev.type == "cuda" and not cache.frozen
+                and not torch.cuda.is_current_stream_capturing() and self._plain_linears()):
+            main = torch.cuda.current_stream(dev)
+            if self._side_stream is None or self._side_stream.device != dev:
+                self._side_stream = torch.cuda.Stream(dev)
+            side = self._side_stream
         g1, g2 = gains(0)
         h1, h2 = ops.sum_residual_norms(x, [], dtype, eps, pre_gain=core.embed_norm.weight, stack=stack, index=0, gain1=g1, gain2=g2)
         for i, layer in enumerate(core.layers):
@@ -488,6 +508,8 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
                 st = cache.run_state(i, latent=True)
             else:
                 st = cache.run_state(i, window=0 if layer.kind == "parallel" else None)
+            if side is not None and layer.mlp is not None:
+                forked = main.record_event()                                 # h2 is ready here; nothing of this layer's mixer is queued yet
             hm = self._conv(h1.view(B, S, -1), 0, cfg.width, layer.canon, None, st.rec, "input", B, S, cache, silu=False, add_input=True)
             hm = hm.view(B * S, -1)
             if layer.kind == "channel_delta":
@@ -497,7 +519,15 @@ class NikedraForCausalLM(PreTrainedModel, GenerationMixin):
             else:
                 y_mix = self._parallel(layer.mixer, hm, st, B, S, cache)
             y_ff = None
-            if layer.mlp is not None:
+            if layer.mlp is not None and side is not None:
+                # behind the mixer's launches in program order, but waiting only for what was on the main stream before them: the
+                # recurrences walk their tokens on a fraction of the SMs, the feed-forward's matrix products take the rest
+                side.wait_event(forked)
+                with torch.cuda.stream(side):
+                    y_ff = layer.mlp(h2) if isinstance(layer.mlp, ClampedMLP) else self._experts(layer.mlp, h2, frozen_step)
+                y_ff.record_stream(main)
+                main.wait_stream(side)
+            elif layer.mlp is not None:
                 y_ff = layer.mlp(h2) if isinstance(layer.mlp, ClampedMLP) else self._experts(layer.mlp, h2, frozen_step)
             g1, g2 = gains(i + 1)
             h1, h2 = ops.sum_residual_norms(x, [y_mix, y_ff], dtype, eps, stack=stack, index=i + 1, coef=layer.dwa, gain1=g1, gain2=g2)

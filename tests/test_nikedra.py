@@ -96,10 +96,10 @@ CONFIGS = {
                  latent=dict(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=48, window=40, scale=0.15),
                  delta=dict(heads=4, kv_heads=1, dim=32, vdim=64, conv=3), left=dict(heads=4, kv_heads=2, dim=32, vdim=16, rot_dims=16, chunk=24, scale=0.2),
                  right=dict(heads=4, vdim=32, state=64, groups=4, norm_groups=4, conv=4), dense=dict(ff=40, limit=2.5), moe=dict(experts=3, top=3, ff=24)),
-    # cache rows of 128 numbers under eight heads (decoding takes the kernel that splits the keys of a shared head over blocks),
+    # a latent of 128 numbers under eight heads (decoding takes the kernel that splits the keys of a shared head over blocks),
     # a window and a chunk longer than a key tile, a recurrent head wider than a warp, many small experts
     "wide": dict(width=72, vocab=300, taps=4, order=("channel_delta", "latent_attention", "parallel"), mlps=("moe", "moe", "dense"),
-                 latent=dict(heads=8, dim=64, rot_dim=32, vdim=48, kv_rank=96, window=70, scale=0.1, base=10000.0),
+                 latent=dict(heads=8, dim=64, rot_dim=32, vdim=48, kv_rank=128, window=70, scale=0.1, base=10000.0),
                  delta=dict(heads=2, kv_heads=2, dim=136, vdim=24, conv=2), left=dict(heads=8, kv_heads=1, dim=64, vdim=128, rot_dims=32, chunk=90, scale=0.12,
                                                                                       factor=16.0, original=64, fast=8.0, slow=2.0, base=1000.0),
                  right=dict(heads=3, vdim=40, state=16, groups=3, norm_groups=1, conv=3), dense=dict(ff=100, limit=1.3), moe=dict(experts=16, top=4, ff=8),
@@ -405,6 +405,18 @@ def test_head_norms_with_their_gates(mixers, cuda_device, dtype):
         assert (_c64(out) - want).abs().max() < tol, parts
     late = O.unit_rms(_c64(o).reshape(n, 5, H * D // 5), eps).reshape(n, H * D) * _c64(w) * gt * torch.sigmoid(gt)
     assert (late - want).abs().max() > 0.1                                  # gating behind the norm would be another function
+    # heads wider than a warp handles well take a block each: the same function
+    H, D = 3, 400
+    o = torch.randn(n, H, D, generator=g).to(cuda_device) * 3
+    gate, w = _rand((n, H * D + 4), g, dtype, cuda_device), _rand((H * D,), g, dtype, cuda_device) + 1.0
+    gt = _c64(gate[:, 4:])
+    out = torch.empty(n, H * D + 2, dtype=dtype, device=cuda_device)
+    mixers.gated_rms_norm(o, gate, 4, w[:D].contiguous(), eps, out, 2, 1.0, sigmoid=True)
+    assert (_c64(out[:, 2:]) - O.unit_rms(_c64(o), eps).reshape(n, H * D) * _c64(w[:D]).repeat(H) * torch.sigmoid(gt)).abs().max() < tol
+    for parts in (1, 2):
+        mixers.gated_rms_norm(o.view(n, parts, H * D // parts), gate, 4, w, eps, out, 2, 0.5, gate_first=True)
+        gated = _c64(o).reshape(n, H * D) * gt * torch.sigmoid(gt)
+        assert (_c64(out[:, 2:]) - 0.5 * O.unit_rms(gated.view(n, parts, -1), eps).reshape(n, H * D) * _c64(w)).abs().max() < tol, parts
 
 
 @pytest.mark.gpu
@@ -492,6 +504,28 @@ def test_windows_and_chunks_in_every_attention_kernel(mixers, cuda_device, dtype
                 want = O.visible_attention(_c64(q.view(B, S, H, D)[b]), _c64(k[b]), _c64(v[b]), scale, held, max(pads[b] - shift, 0), window, chunk,
                                            origin=pads[b] - shift)
                 assert (_c64(got.view(B, S, H, Dv)[b]) - want).abs().max() < tol, (shift, pads, window, chunk, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,S,tc", [(torch.float32, 1, False), (torch.bfloat16, 1, True), (torch.bfloat16, 9, True), (torch.bfloat16, 30, True)])
+def test_values_that_are_the_first_channels_of_the_key_rows(mixers, cuda_device, dtype, S, tc):
+    """one cache row per position, shared by eight heads: the whole row is the key, its first 128 numbers are the value (the
+    decoding form of the latent attention) -- in the general kernel, the split-key kernel and the prompt kernel"""
+    g = torch.Generator().manual_seed(S)
+    B, H, D, Dv, held = 2, 8, 144, 128, 300
+    L = held + S
+    q = _rand((B * S, H, D), g, dtype, cuda_device)
+    rows = _rand((B, L + 5, 1, D), g, dtype, cuda_device)
+    pads = [0, 7]
+    pad = torch.tensor(pads, dtype=torch.int32, device=cuda_device)
+    if tc and S <= 16:
+        from ipex_llm_b200.ggml.model import mixers_cpp
+        assert mixers_cpp.lib().mixers_softmax_attention_workspace(mixers_cpp.dtype_code(dtype), B, S, H, 1, D, Dv) > 0
+    for window in (0, 70, 301):
+        got = mixers.softmax_attention(q, rows, rows[..., :Dv], B, S, H, held, 0, pad, window, 0.1, tensor_cores=tc)
+        for b in range(B):
+            want = O.visible_attention(_c64(q.view(B, S, H, D)[b]), _c64(rows[b]), _c64(rows[b, ..., :Dv]), 0.1, held, pads[b], window)
+            assert (_c64(got.view(B, S, H, Dv)[b]) - want).abs().max() < (2e-5 if dtype == torch.float32 else 0.02), (window, b)
 
 
 @pytest.mark.gpu
@@ -785,11 +819,11 @@ def test_greedy_generate_matches_the_oracle(tmp_path, cuda_device, name):
 @pytest.mark.gpu
 def test_recorded_step_of_a_16_bit_model_equals_the_eager_loop(tmp_path, cuda_device, monkeypatch):
     """a bf16 model whose latent attention decodes through the kernel that splits the keys of a shared head over blocks (8 heads
-    on one cache row of 128 numbers): the replayed step reads the cache length from the device and must produce the tokens of the
+    on one cache row whose first 128 numbers are the values): the replayed step reads the cache length from the device and must produce the tokens of the
     loop that passes it from the host; states and tails are updated in place by both; the window passes over decoded tokens"""
     cfg, w, model = build(tmp_path, "wide", torch.bfloat16, cuda_device)
     from ipex_llm_b200.ggml.model import mixers_cpp
-    assert mixers_cpp.lib().mixers_softmax_attention_workspace(mixers_cpp.dtype_code(torch.bfloat16), 2, 1, 8, 1, 128, 128) > 0
+    assert mixers_cpp.lib().mixers_softmax_attention_workspace(mixers_cpp.dtype_code(torch.bfloat16), 2, 1, 8, 1, 160, 128) > 0
     prompts = torch.tensor([tokens_for(cfg, 70, 1), [0] * 30 + tokens_for(cfg, 40, 2)], device=cuda_device)
     mask = torch.tensor([[1] * 70, [0] * 30 + [1] * 40], device=cuda_device)
     replayed = model.generate(prompts, attention_mask=mask, max_new_tokens=80, do_sample=False)
@@ -859,3 +893,24 @@ def test_trace_runner_replays_batches_and_gives_rows_back(tmp_path, cuda_device)
     for i in (0, 1, 3, 4, 5):
         assert_close(rows(1 + i), torch.stack([full["a"][25 + i], full["b"][6 + i]][:2 if i < 4 else 1]), torch.float32)
     assert_close(rows(7), torch.stack([full["c"][19], full["d"][0], full["d"][8]]), torch.float32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,dtype", [("tile", torch.bfloat16), ("odd", torch.float32), ("wide", torch.bfloat16)])
+def test_feed_forward_beside_the_mixer_changes_nothing(tmp_path, cuda_device, name, dtype):
+    """long prompts run every layer's feed-forward on a second stream while the mixer runs on the first: the same kernels on the
+    same numbers, so the logits are the same bit for bit, call after call (storage that one stream frees is not handed to the
+    other too early), and decoding continues from the state such a prompt left"""
+    from ipex_llm_b200.transformers.models import nikedra
+    cfg, w, model = build(tmp_path, name, dtype, cuda_device)
+    ids = torch.tensor([tokens_for(cfg, 130, s) for s in (1, 2, 3)], device=cuda_device)
+    assert ids.numel() >= nikedra.OVERLAP_MIN_TOKENS
+    with torch.no_grad():
+        model.overlap_feed_forward = False
+        want = model(input_ids=ids, use_cache=True)
+        want_next = model(input_ids=ids[:, :1], past_key_values=want.past_key_values, use_cache=True).logits
+        model.overlap_feed_forward = True
+        for _ in range(4):
+            got = model(input_ids=ids, use_cache=True)
+            assert model._side_stream is not None and torch.equal(got.logits, want.logits)
+        assert torch.equal(model(input_ids=ids[:, :1], past_key_values=got.past_key_values, use_cache=True).logits, want_next)
