@@ -104,12 +104,18 @@ CONFIGS = {
                                                                                       factor=16.0, original=64, fast=8.0, slow=2.0, base=1000.0),
                  right=dict(heads=3, vdim=40, state=16, groups=3, norm_groups=1, conv=3), dense=dict(ff=100, limit=1.3), moe=dict(experts=16, top=4, ff=8),
                  logit_scale=0.1),
+    # sizes that are multiples of nothing: rows that start off every vector boundary, five heads, three norm parts of five channels,
+    # a window of three and a chunk of two tokens, every expert for every token, both low ranks of one
+    "awkward": dict(width=52, vocab=37, taps=2, order=("parallel", "channel_delta", "latent_attention"), mlps=("moe", "dense", "moe"),
+                    latent=dict(heads=5, dim=6, rot_dim=2, vdim=3, kv_rank=7, window=3, scale=0.5), delta=dict(heads=3, kv_heads=3, dim=5, vdim=9, conv=3),
+                    left=dict(heads=3, kv_heads=1, dim=6, vdim=5, rot_dims=2, chunk=2, scale=0.4), right=dict(heads=5, vdim=3, state=7, groups=5, norm_groups=3, conv=2),
+                    dense=dict(ff=25, limit=0.4), moe=dict(experts=2, top=2, ff=11), logit_scale=2.0),
 }
 
 
 def make(name, seed=0):
     cfg = O.random_config(**CONFIGS[name])
-    return cfg, O.random_weights(cfg, seed + 1, ranks=(3, 1) if name == "plain" else (5, 3))
+    return cfg, O.random_weights(cfg, seed + 1, ranks={"plain": (3, 1), "awkward": (1, 1)}.get(name, (5, 3)))
 
 
 def w64(w):
