@@ -104,6 +104,13 @@ CONFIGS = {
                                                                                       factor=16.0, original=64, fast=8.0, slow=2.0, base=1000.0),
                  right=dict(heads=3, vdim=40, state=16, groups=3, norm_groups=1, conv=3), dense=dict(ff=100, limit=1.3), moe=dict(experts=16, top=4, ff=8),
                  logit_scale=0.1),
+    # head sizes of a served model on a narrow stream: heads of 128, a latent of 512 + 64 rotated (decoding reads cache rows of 576 as
+    # keys and their first 512 numbers as values in the split-key kernel), a state of 128 x 64
+    "full": dict(width=128, vocab=97, taps=4, order=("latent_attention", "channel_delta", "parallel"), mlps=("moe", "dense", "moe"),
+                 latent=dict(heads=4, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=50, scale=0.07, base=10000.0),
+                 delta=dict(heads=4, kv_heads=2, dim=128, vdim=128, conv=4), left=dict(heads=8, kv_heads=2, dim=128, vdim=128, rot_dims=64, chunk=32, scale=0.09,
+                                                                                      factor=8.0, original=64, fast=16.0, slow=1.0, base=500000.0),
+                 right=dict(heads=4, vdim=64, state=128, groups=2, norm_groups=2, conv=4), dense=dict(ff=256, limit=7.0), moe=dict(experts=3, top=2, ff=64)),
     # sizes that are multiples of nothing: rows that start off every vector boundary, five heads, three norm parts of five channels,
     # a window of three and a chunk of two tokens, every expert for every token, both low ranks of one
     "awkward": dict(width=52, vocab=37, taps=2, order=("parallel", "channel_delta", "latent_attention"), mlps=("moe", "dense", "moe"),
