@@ -635,7 +635,7 @@ def run_ours(args):
                          "weights_GBps_in_generate": algorithmic_bytes() / (ms_dev * 1e-3) / 1e9,
                          "frac_of_hbm_peak_in_generate": algorithmic_bytes() / (ms_dev * 1e-3) / 1e9 / peak},
             "linear_stream": {"ms_per_token": ms_stream, "tok_per_s": 1e3 / ms_stream, "launches_per_token": stream_launches,
-                              "GBps": achieved, "note": "round 1's headline: LowBitLinear launches only, constant activations"},
+                              "GBps": achieved, "note": "the first headline: LowBitLinear launches only, constant activations"},
         },
         "clocks": clocks.summary(),
     }

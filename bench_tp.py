@@ -108,7 +108,7 @@ def main():
             step()
         torch.cuda.synchronize()
         log("eager steps done")
-        # torch's ProcessGroupNCCL collectives hung under CUDA-graph capture on the gpurun box (round 1, unresolved):
+        # torch's ProcessGroupNCCL collectives hung under CUDA-graph capture on a B200 box (cause not found):
         # with collectives the step is launched eagerly (launch-bound: the number is a lower bound)
         if not args.no_graph and (world == 1 or args.no_allreduce or peer is not None):
             graph = torch.cuda.CUDAGraph()

@@ -107,7 +107,7 @@ int lowbit_dequantize_device_layout_cuda(const void* d_src, void* d_dst, int64_t
  * the dequantise kernels (bit-exact against the oracle). */
 int lowbit_dequantize_rows_cuda(const void* d_w, int qtype, int64_t rows, int64_t k, const void* d_ids,
                                 int ids_dtype, int64_t n_ids, void* d_out, int out_dtype, void* stream);
-/* ---- FP8 key/value cache (SURVEY 8f): DynamicFp8Cache (transformers/kv.py:33-77) keeps K and V as uint8
+/* ---- FP8 key/value cache: DynamicFp8Cache (transformers/kv.py:33-77) keeps K and V as uint8
  * [batch, kv_heads, len, head_dim].  The reference's xe_addons kernels are closed; the byte format here is
  * BUILD-DEFINED: one e5m2 code per element (round to nearest even, saturating), no scales.
  * Tensors are 4-D views [B][H][S][D] with D contiguous; strides[3] = element strides of B, H, S (host array).

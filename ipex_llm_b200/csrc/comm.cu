@@ -1,5 +1,5 @@
 // comm.cu -- all-reduce(sum) of the small [M, hidden] results of the row-parallel linears in tensor-parallel decode
-// (SURVEY 8e: reference low_bit_linear.py:715-725 calls torch.distributed / the DeepSpeed group all_reduce after
+// (reference low_bit_linear.py:715-725 calls torch.distributed / the DeepSpeed group all_reduce after
 // o_proj and down_proj: 2 per layer, 16 - 32 KiB at M = 1).  One process per GPU; every rank owns one buffer
 // (cudaMalloc, exported with cudaIpcGetMemHandle, mapped by the peers with cudaIpcOpenMemHandle):
 //     [epochs: COMM_MAX_CTAS x u32][status u32] ... [slot 0: world x inbox][slot 1: world x inbox]

@@ -16,7 +16,7 @@
 //   warp 1   MMA      : the whole warp runs the issue loop in warp-uniform control flow and one elected lane
 //                       issues tcgen05.mma.cta_group::1.kind::f16 (M=128, N=128, K=16; 4 per k-block per token
 //                       sub-tile), accumulators in TMEM (128*MT columns), tcgen05.commit releases the stage and
-//                       finally signals the epilogue.  (Round 2: with the loop inside a single-lane branch every
+//                       finally signals the epilogue.  (With the loop inside a single-lane branch every
 //                       operand was moved into a uniform register per instruction, ~45 ns per MMA: the issue
 //                       thread, not shared-memory bandwidth, set the pace -- 1017 -> 1262 TFLOP/s.)
 // The expanded weights never touch HBM; both token sub-tiles reuse one expanded B tile.

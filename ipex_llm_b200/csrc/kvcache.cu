@@ -1,4 +1,4 @@
-// kvcache.cu -- FP8 key/value cache and the decode attention that reads it (SURVEY 8f rank 3).
+// kvcache.cu -- FP8 key/value cache and the decode attention that reads it.
 //
 // Reference: DynamicFp8Cache (transformers/kv.py:33-77) keeps K and V as uint8 [batch, kv_heads, len, head_dim]
 // (models/utils.py:103-139: init_fp8_kv_cache / append_fp8_kv_cache -> xe_addons.quantize_key_value, restore ->

@@ -568,7 +568,7 @@ static int launch_recurrence(RecArgs a, cudaStream_t stream) {
     if (bytes > 160 * 1024) return launch_recurrence_few<T, MODE>(a, stream);  // very wide heads: stages of fewer tokens, unpipelined
     a.lpc = lpc; a.tc = REC_TC;
     dim3 grid((a.vdim + cols_blk - 1) / cols_blk, a.heads, a.B);
-    const bool pair = MODE == 2 && (long)grid.x * grid.y * grid.z > 148 && 2 * bytes <= 200 * 1024;
+    const bool pair = (MODE == 2 || MODE == 3) && (long)grid.x * grid.y * grid.z > 148 && 2 * bytes <= 200 * 1024;
     auto kernel = r == 16 ? (pair ? linear_recurrence_kernel<T, MODE, 16, 2> : linear_recurrence_kernel<T, MODE, 16, 0>)
                           : (pair ? linear_recurrence_kernel<T, MODE, 32, 2> : linear_recurrence_kernel<T, MODE, 32, 0>);
     static size_t allowed[4] = {48 * 1024, 48 * 1024, 48 * 1024, 48 * 1024};   // per instantiation: raised once, outside any capture

@@ -1,5 +1,5 @@
 // rope.cu -- in-place rotary position embedding of the query and key heads that the merged qkv projection produced
-// (second half: reference models/llama.py:151-165 and 40 other decoders call
+// (reference models/llama.py:151-165 and 40 other decoders call
 // xe_addons.rotary_half_inplaced / rotary_two_inplaced(inv_freq, position_ids, q, k) and
 // rotary_half_with_cache_inplaced / rotary_two_with_cache_inplaced(q, k, cos, sin[, half_layout]),
 // models/common.py:354-367).

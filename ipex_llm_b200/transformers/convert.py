@@ -7,7 +7,7 @@ reference's ipex_llm/transformers/convert.py (CV below) that CONSTRUCTS the hot 
 hot path's configs name, llama (CV:1000-1003, 1327-1340) and mistral (CV:1007-1009, 1724-1735): q/k/v merged
 into one ``qkv_proj`` before quantisation, and the attention / MLP / RMSNorm / model forwards replaced by the ones
 in ``transformers/models`` that call the fused operators.  ``optimize_model=False`` leaves the stock Hugging Face
-forwards on top of ``LowBitLinear``.  The reference's 40 other model families are out of scope (SURVEY 2.1).
+forwards on top of ``LowBitLinear``.  The reference's 40 other model families are out of scope.
 """
 import types
 import logging
@@ -110,8 +110,8 @@ def _replace_with_low_bit_linear(model, qtype, modules_to_not_convert=None, conv
             has_been_replaced = True
             module.weight = None
         elif _is_fused_experts(module) and module.gate_up_proj.shape[2] % 64 == 0 and module.down_proj.shape[2] % 64 == 0:
-            # transformers >= 5 mixture-of-experts layers: every expert of the layer in two 3-D parameters (SURVEY 7,
-            # "hard parts"); they become per-expert LowBitLinear modules, quantised like any other linear
+            # transformers >= 5 mixture-of-experts layers: every expert of the layer in two 3-D parameters;
+            # they become per-expert LowBitLinear modules, quantised like any other linear
             from ipex_llm_b200.transformers.models.mixtral import LowBitExperts
             model._modules[name] = LowBitExperts.from_fused(module, qtype, convert_shape_only, enable_scale_search)
             has_been_replaced = True

@@ -9,7 +9,7 @@ Parity status: byte-level parity with the reference's closed binary is UNPINNED 
 binary and any golden vectors are absent from /root/reference).  sym_int4/asym_int4 are
 pinned against gguf.quants and against vectors generated from the reference's own
 in-repo Python statements (tests/golden/make_golden.py); nf4/fp8/fp6 are build-defined.
-See lowbit_oracle.c header and DESIGN.md.
+See the header of lowbit_oracle.c.
 """
 import ctypes
 import os

@@ -8,7 +8,7 @@
  * `--impl reference` legs may load this file's shared object.  The product
  * (ipex_llm_b200/csrc) never includes, links or calls anything from here.
  *
- * PARITY STATUS (see DESIGN.md "Oracle"):
+ * PARITY STATUS:
  *   - the reference's own binary for this path is NOT in /root/reference and the
  *     reference has no golden vectors for it, so byte-level parity with the
  *     closed binary is UNPINNED;
@@ -22,8 +22,7 @@
  *         transformers/gguf/gguf.py:273-296 (Q4_0 / Q4_1 dequantisation) and
  *         transformers/convert.py:382-456 (convert_gptq -> asym_int4 records);
  *   - nf4 / fp8_e4m3 / fp8_e5m2 / fp6 have no statement of layout or arithmetic
- *     anywhere in the reference: they are BUILD-DEFINED here (FORMAT section of
- *     DESIGN.md) and the oracle is the specification the CUDA kernels must meet.
+ *     anywhere in the reference: they are BUILD-DEFINED here, and the oracle is the specification the CUDA kernels must meet.
  *
  * Block record (canonical / CPU / on-disk layout), row-major [rows][k/QK]:
  *   d (fp16) [, m (fp16)] , codes            -- convert.py:448-453 (d, m, qs order)

@@ -172,7 +172,7 @@ def test_config5_mixtral_moe_decode(lbl, cuda_device):
 
 
 def test_config5_mixtral_moe_tp_inside_experts(lbl, cuda_device):
-    """SURVEY 8e, MoE sharding (1): tensor parallelism inside every expert -- w1 / w3 column-sharded, w2 row-sharded
+    """MoE sharding (1): tensor parallelism inside every expert -- w1 / w3 column-sharded, w2 row-sharded
     (14336 / 8 = 1792 = 28 blocks), the ranks' outputs summed by the same all-reduce as the dense layers.  Every
     rank's fused one-token MoE is run on this one GPU; the sum over ranks must equal the unsharded MoE up to the
     summation order and the fp16 rounding of the intermediate activations."""

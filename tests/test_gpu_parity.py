@@ -1,6 +1,6 @@
 """GPU parity tests: the sm_100a kernels behind the C ABI against the CPU oracle.
 
-Bars (SURVEY 8c):
+Bars:
   * packed bytes (quantise, relayout round trip): bit-exact;
   * dequantise: bit-exact (same fp32 formula, no contraction);
   * matmul vs mode-B oracle: |diff| <= 2e-6 * sum_k |x_k w_k| + 1e-30 for every element when the

@@ -1,4 +1,4 @@
-"""FP8 key/value cache and decode attention (SURVEY 8f rank 3; reference transformers/kv.py:33-77,
+"""FP8 key/value cache and decode attention (reference transformers/kv.py:33-77,
 models/utils.py:103-190, models/common.py:250-306).
 
 The byte format is build-defined (e5m2, round to nearest even): checked against torch.float8_e5m2.  The

@@ -1,4 +1,4 @@
-"""GPU parity of the fused decode ops built on the dequant-GEMV (SURVEY 8(a16), 8(a17)):
+"""GPU parity of the fused decode ops built on the dequant-GEMV:
 
   * mlp_forward  = xe_linear.mlp_forward_xpu  (models/common.py:146-161)
   * moe_forward  = xe_linear.moe_forward_vec   (models/common.py:341-354 fast path)

@@ -1,4 +1,4 @@
-"""The library's own all-reduce for tensor-parallel decode (csrc/comm.cu, SURVEY 8e; the reference calls
+"""The library's own all-reduce for tensor-parallel decode (csrc/comm.cu; the reference calls
 torch.distributed / DeepSpeed all_reduce at low_bit_linear.py:715-725).  2, 4 and 8 ranks, one process per GPU
 (each case is skipped on a box with fewer GPUs).  Expected values are the rank-ordered fp32 sums, rounded once to the
 tensor's dtype: the kernel must match them bit for bit, on every rank.

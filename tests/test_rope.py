@@ -1,4 +1,4 @@
-"""In-place rotary position embedding (second half; reference models/llama.py:151-165,
+"""In-place rotary position embedding (reference models/llama.py:151-165,
 models/chatglm2.py:251, models/common.py:354-367).  Reference: the rotation evaluated in float64 from fp32
 angles (position * inv_freq in fp32, as transformers computes them) or from the given tables; the kernel works
 in fp32 and rounds once, so the tolerance is one rounding of the output dtype plus the fp32 sin / cos error.

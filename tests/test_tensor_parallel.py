@@ -1,4 +1,4 @@
-"""Tensor-parallel host logic on CPU (SURVEY 8e): sharding of packed weights commutes with
+"""Tensor-parallel host logic on CPU: sharding of packed weights commutes with
 quantisation, and a world_size-2 gloo run reproduces the unsharded result with the all-reduce
 where the reference puts it (after the matmul, before the bias; low_bit_linear.py:715-725).
 
